@@ -1,5 +1,6 @@
 from .base import ConfigError, ConfigReader, read_json
 from .generation import GenerationDefaults, read_generation_defaults
+from .nunivik import NunivikConfig
 from .qwen2 import Qwen2Config
 
-__all__ = ["ConfigError", "ConfigReader", "read_json", "GenerationDefaults", "read_generation_defaults", "Qwen2Config"]
+__all__ = ["ConfigError", "ConfigReader", "read_json", "GenerationDefaults", "read_generation_defaults", "Qwen2Config", "NunivikConfig"]

@@ -6,6 +6,9 @@
 // into steps or on the rest of the batch. The formula is the reference's: q head h reads kv head
 // h / group, scores (q.k) * scale for key position <= query position, softmax, weighted sum of values
 // (helios/crates/helios-hal/src/reference.rs:118-156; kernels/elementwise.cu:64-118).
+// Beyond the reference: keys and values may have different sizes per head and lie anywhere in a page
+// (the launcher gets their two base pointers and the strides of a page, a head and a token), and a
+// score may be capped smoothly, s <- cap * tanh(s / cap), before the softmax (cap 0 = no cap).
 #include "common.cuh"
 
 namespace {
@@ -13,10 +16,11 @@ constexpr int TILE = 64, THREADS = 128, GMAX = 8, DMAX = 256;
 
 template <typename T>
 __global__ void __launch_bounds__(THREADS) attention_generic_kernel(
-    const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride, const T* __restrict__ cache,
+    const T* __restrict__ q, int q_stride, T* __restrict__ out, int out_stride, const T* __restrict__ k_cache,
+    const T* __restrict__ v_cache, size_t page_stride, size_t head_stride, int token_stride,
     const int* __restrict__ block_table, int table_width, const int* __restrict__ token_row,
-    const int* __restrict__ positions, int heads, int kv_heads, int head_dim, int page_size, int pages, float scale,
-    int window, int* status) {
+    const int* __restrict__ positions, int heads, int kv_heads, int head_dim, int v_dim, int page_size, int pages, float scale,
+    float softcap, int window, int* status) {
     __shared__ float qs[GMAX][DMAX];
     __shared__ float score[GMAX][TILE];
     __shared__ float m_run[GMAX], l_run[GMAX], alpha[GMAX];
@@ -43,8 +47,6 @@ __global__ void __launch_bounds__(THREADS) attention_generic_kernel(
         for (int c = 0; c < DMAX / THREADS; ++c) acc[hh][c] = 0.f;
 
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    const size_t head_stride = (size_t)page_size * head_dim;
-    const size_t page_stride = 2 * (size_t)kv_heads * head_stride;
     bool bad_page = false;
     __syncthreads();
 
@@ -69,7 +71,7 @@ __global__ void __launch_bounds__(THREADS) attention_generic_kernel(
 #pragma unroll
             for (int hh = 0; hh < GMAX; ++hh) part[hh] = 0.f;
             if (page >= 0) {
-                const T* kp = cache + (size_t)page * page_stride + (size_t)kvh * head_stride + (size_t)(j % page_size) * head_dim;
+                const T* kp = k_cache + (size_t)page * page_stride + (size_t)kvh * head_stride + (size_t)(j % page_size) * token_stride;
                 for (int d = lane; d < head_dim; d += 32) {
                     const float kv = to_float(kp[d]);
 #pragma unroll
@@ -81,7 +83,11 @@ __global__ void __launch_bounds__(THREADS) attention_generic_kernel(
             for (int hh = 0; hh < GMAX; ++hh) {
                 if (hh < g) {
                     const float s = warp_sum(part[hh]);
-                    if (lane == 0) score[hh][jj] = page >= 0 ? s * scale : -INFINITY;
+                    if (lane == 0) {
+                        float capped = s * scale;
+                        if (softcap > 0.f) capped = softcap * tanhf(capped / softcap);
+                        score[hh][jj] = page >= 0 ? capped : -INFINITY;
+                    }
                 }
             }
         }
@@ -109,7 +115,7 @@ __global__ void __launch_bounds__(THREADS) attention_generic_kernel(
 #pragma unroll
         for (int c = 0; c < DMAX / THREADS; ++c) {
             const int d = tid + c * THREADS;
-            if (d < head_dim) {
+            if (d < v_dim) {
 #pragma unroll
                 for (int hh = 0; hh < GMAX; ++hh)
                     if (hh < g) acc[hh][c] *= alpha[hh];
@@ -117,8 +123,8 @@ __global__ void __launch_bounds__(THREADS) attention_generic_kernel(
                     const int page = tile_page[jj];
                     if (page < 0) continue;
                     const int j = base + jj;
-                    const float vv = to_float(cache[(size_t)page * page_stride + (size_t)(kv_heads + kvh) * head_stride +
-                                                    (size_t)(j % page_size) * head_dim + d]);
+                    const float vv = to_float(v_cache[(size_t)page * page_stride + (size_t)kvh * head_stride +
+                                                      (size_t)(j % page_size) * token_stride + d]);
 #pragma unroll
                     for (int hh = 0; hh < GMAX; ++hh)
                         if (hh < g) acc[hh][c] = fmaf(score[hh][jj], vv, acc[hh][c]);
@@ -131,12 +137,12 @@ __global__ void __launch_bounds__(THREADS) attention_generic_kernel(
 #pragma unroll
     for (int c = 0; c < DMAX / THREADS; ++c) {
         const int d = tid + c * THREADS;
-        if (d < head_dim) {
+        if (d < v_dim) {
 #pragma unroll
             for (int hh = 0; hh < GMAX; ++hh)
                 if (hh < g) {
                     const float l = l_run[hh];
-                    out[(size_t)t * out_stride + (size_t)(kvh * group + g0 + hh) * head_dim + d] =
+                    out[(size_t)t * out_stride + (size_t)(kvh * group + g0 + hh) * v_dim + d] =
                         from_float<T>(l > 0.f ? acc[hh][c] / l : 0.f);
                 }
         }
@@ -144,22 +150,40 @@ __global__ void __launch_bounds__(THREADS) attention_generic_kernel(
 }
 }  // namespace
 
-HB_EXPORT int hb_attention_generic(const void* q, int q_stride, void* out, int out_stride, int is_bf16, const void* cache,
+// Keys at k_cache[page * page_stride + kv_head * head_stride + place * token_stride + i], i < head_dim; values likewise
+// from v_cache with i < v_dim (strides in elements).
+HB_EXPORT int hb_attention_general(const void* q, int q_stride, void* out, int out_stride, int is_bf16, const void* k_cache,
+                                   const void* v_cache, long long page_stride, long long head_stride, int token_stride,
                                    const int* block_table, int table_width, const int* token_row, const int* positions,
-                                   int tokens, int heads, int kv_heads, int head_dim, int page_size, int pages, float scale,
-                                   int window, int* status, cudaStream_t stream) {
+                                   int tokens, int heads, int kv_heads, int head_dim, int v_dim, int page_size, int pages, float scale,
+                                   float softcap, int window, int* status, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (head_dim <= 0 || head_dim > DMAX || kv_heads <= 0 || heads % kv_heads || page_size <= 0) return HB_UNSUPPORTED_SIZE;
+    if (head_dim <= 0 || head_dim > DMAX || v_dim <= 0 || v_dim > DMAX || kv_heads <= 0 || heads % kv_heads || page_size <= 0)
+        return HB_UNSUPPORTED_SIZE;
     const int group = heads / kv_heads;
     dim3 grid(tokens, kv_heads, (group + GMAX - 1) / GMAX);
     if (grid.y > 65535 || grid.z > 65535) return HB_UNSUPPORTED_SIZE;
     if (is_bf16)
         attention_generic_kernel<<<grid, THREADS, 0, stream>>>((const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
-                                                               (const __nv_bfloat16*)cache, block_table, table_width, token_row,
-                                                               positions, heads, kv_heads, head_dim, page_size, pages, scale, window, status);
+                                                               (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (size_t)page_stride,
+                                                               (size_t)head_stride, token_stride, block_table, table_width, token_row,
+                                                               positions, heads, kv_heads, head_dim, v_dim, page_size, pages, scale, softcap, window, status);
     else
-        attention_generic_kernel<<<grid, THREADS, 0, stream>>>((const float*)q, q_stride, (float*)out, out_stride, (const float*)cache,
+        attention_generic_kernel<<<grid, THREADS, 0, stream>>>((const float*)q, q_stride, (float*)out, out_stride, (const float*)k_cache,
+                                                               (const float*)v_cache, (size_t)page_stride, (size_t)head_stride, token_stride,
                                                                block_table, table_width, token_row, positions, heads, kv_heads,
-                                                               head_dim, page_size, pages, scale, window, status);
+                                                               head_dim, v_dim, page_size, pages, scale, softcap, window, status);
     return launch_status();
+}
+
+// Keys and values of one size in pages of [2, kv_heads, page_size, head_dim], no cap.
+HB_EXPORT int hb_attention_generic(const void* q, int q_stride, void* out, int out_stride, int is_bf16, const void* cache,
+                                   const int* block_table, int table_width, const int* token_row, const int* positions,
+                                   int tokens, int heads, int kv_heads, int head_dim, int page_size, int pages, float scale,
+                                   int window, int* status, cudaStream_t stream) {
+    const long long head_stride = (long long)page_size * head_dim;
+    const size_t element = is_bf16 ? 2 : 4;
+    return hb_attention_general(q, q_stride, out, out_stride, is_bf16, cache, (const char*)cache + (size_t)kv_heads * head_stride * element,
+                                2 * (long long)kv_heads * head_stride, head_stride, head_dim, block_table, table_width, token_row, positions,
+                                tokens, heads, kv_heads, head_dim, head_dim, page_size, pages, scale, 0.f, window, status, stream);
 }

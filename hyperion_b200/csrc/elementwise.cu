@@ -10,7 +10,7 @@
 // ---------------------------------------------------------------- embedding
 template <typename TW>
 __global__ void embedding_kernel(const TW* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
-                                 int hidden, int vocab, int* status) {
+                                 int hidden, int vocab, float scale, int* status) {
     const int t = blockIdx.x;
     const int id = ids[t];
     if (id < 0 || id >= vocab) {
@@ -19,12 +19,12 @@ __global__ void embedding_kernel(const TW* __restrict__ table, const int* __rest
         return;
     }
     const TW* row = table + (size_t)id * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)t * hidden + i] = to_float(row[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)t * hidden + i] = to_float(row[i]) * scale;
 }
 
 // bfloat16 rows whose width is a multiple of 8: one 16-byte load and two 16-byte stores per thread.
 __global__ void embedding_bf16x8_kernel(const __nv_bfloat16* __restrict__ table, const int* __restrict__ ids, float* __restrict__ out,
-                                        int hidden, int vocab, int* status) {
+                                        int hidden, int vocab, float scale, int* status) {
     const int t = blockIdx.x;
     const int id = ids[t];
     const bool ok = id >= 0 && id < vocab;
@@ -36,26 +36,27 @@ __global__ void embedding_bf16x8_kernel(const __nv_bfloat16* __restrict__ table,
             const uint4 v = *reinterpret_cast<const uint4*>(row + i);
             const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
             const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]), f2 = __bfloat1622float2(h[2]), f3 = __bfloat1622float2(h[3]);
-            a = make_float4(f0.x, f0.y, f1.x, f1.y);
-            b = make_float4(f2.x, f2.y, f3.x, f3.y);
+            a = make_float4(f0.x * scale, f0.y * scale, f1.x * scale, f1.y * scale);
+            b = make_float4(f2.x * scale, f2.y * scale, f3.x * scale, f3.y * scale);
         }
         *reinterpret_cast<float4*>(out + (size_t)t * hidden + i) = a;
         *reinterpret_cast<float4*>(out + (size_t)t * hidden + i + 4) = b;
     }
 }
 
+// out[t] = table[ids[t]] * scale, in float (scale 1 leaves the table's values as they are).
 HB_EXPORT int hb_embedding(const void* table, int table_is_bf16, const int* ids, float* out, int tokens, int hidden,
-                           int vocab, int* status, cudaStream_t stream) {
+                           int vocab, float scale, int* status, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (table_is_bf16 && hidden % 8 == 0 && (((uintptr_t)table | (uintptr_t)out) & 15) == 0) {
         const int threads = min(512, ((hidden / 8 + 31) / 32) * 32);
-        embedding_bf16x8_kernel<<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
+        embedding_bf16x8_kernel<<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, scale, status);
         return launch_status();
     }
     if (table_is_bf16)
-        embedding_kernel<<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, status);
+        embedding_kernel<<<tokens, 256, 0, stream>>>((const __nv_bfloat16*)table, ids, out, hidden, vocab, scale, status);
     else
-        embedding_kernel<<<tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden, vocab, status);
+        embedding_kernel<<<tokens, 256, 0, stream>>>((const float*)table, ids, out, hidden, vocab, scale, status);
     return launch_status();
 }
 
@@ -571,5 +572,54 @@ HB_EXPORT int hb_kv_store(const void* src, int is_bf16, int tokens, int stride, 
     else
         kv_store_kernel<<<tokens, 256, 0, stream>>>((const float*)src, stride, k_offset, v_offset, (float*)cache, block_table,
                                                     table_width, token_row, positions, kv_heads, head_dim, page_size, pages, status);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------- RMSNorm of a sublayer's output, added to the stream
+// h[t] += y[t] / sqrt(mean(y[t]^2) + eps) * weight, for blocks that normalise what a sublayer returns instead of what it
+// reads.  `copy` (optional) receives the new h[t] in the activation type: the next sublayer's input.  The sum of squares is
+// taken in a fixed order per row, so a row's result depends on nothing else in the launch.
+template <typename TY, typename TC>
+__global__ void rmsnorm_add_kernel(float* __restrict__ h, const TY* __restrict__ y, const float* __restrict__ weight,
+                                   TC* __restrict__ copy, int hidden, float eps) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x;
+    float* hrow = h + (size_t)t * hidden;
+    const TY* yrow = y + (size_t)t * hidden;
+    float sum = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = to_float(yrow[i]);
+        sum = fmaf(v, v, sum);
+    }
+    const float total = block_sum(sum, scratch);
+    const float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = hrow[i] + to_float(yrow[i]) * inv * weight[i];
+        hrow[i] = v;
+        if (copy) copy[(size_t)t * hidden + i] = from_float<TC>(v);
+    }
+}
+
+HB_EXPORT int hb_rmsnorm_add(float* h, const void* y, int y_is_bf16, const float* weight, void* copy, int tokens, int hidden,
+                             float eps, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    if (y_is_bf16)
+        rmsnorm_add_kernel<<<tokens, threads, 0, stream>>>(h, (const __nv_bfloat16*)y, weight, (__nv_bfloat16*)copy, hidden, eps);
+    else
+        rmsnorm_add_kernel<<<tokens, threads, 0, stream>>>(h, (const float*)y, weight, (float*)nullptr, hidden, eps);
+    return launch_status();
+}
+
+// The float stream in the activation type (bfloat16): what the first sublayer of a model reads.
+__global__ void stream_copy_kernel(const float* __restrict__ h, __nv_bfloat16* __restrict__ copy, size_t count) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x)
+        copy[i] = __float2bfloat16_rn(h[i]);
+}
+
+HB_EXPORT int hb_stream_copy(const float* h, void* copy, long long count, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    const int blocks = (int)((count + 255) / 256 < 4096 ? (count + 255) / 256 : 4096);
+    stream_copy_kernel<<<blocks, 256, 0, stream>>>(h, (__nv_bfloat16*)copy, (size_t)count);
     return launch_status();
 }

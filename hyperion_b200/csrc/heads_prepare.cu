@@ -1,0 +1,106 @@
+// What happens to a token's projected heads between the q/k/v product and attention, in one pass:
+//   * query and key heads: RMS norm over the head with a weight shared by all heads (optional),
+//   * rotation of the first `rot_dims` dimensions of query and key heads, dimension 2i paired with 2i+1,
+//     by the angle position * inv_freq[i] (optional); the rest of the head passes unchanged,
+//   * values: v <- (1 - lambda) v + lambda v_first, v_first being another layer's values of the same
+//     token and lambda one scalar on the device (optional),
+//   * keys and (mixed) values written to their cache page; queries written back in place.
+// Norm, angle, sine and cosine and the mix are float; a value is rounded once, when it is stored.
+// The row is [q heads x head_dim | k heads x head_dim | v heads x v_dim].  The cache is addressed
+// by two base pointers and the strides of a page, a head and a token (in elements), so keys and
+// values may share a page in any arrangement.
+#include "common.cuh"
+
+namespace {
+constexpr int THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(THREADS) heads_prepare_kernel(
+    T* __restrict__ x, int stride, int q_heads, int kv_heads, int head_dim, int v_dim, const float* __restrict__ q_norm,
+    const float* __restrict__ k_norm, float eps, const float* __restrict__ inv_freq, int rot_dims, const int* __restrict__ positions,
+    const T* __restrict__ v_first, int v_first_stride, const float* __restrict__ lambda, T* __restrict__ k_cache, T* __restrict__ v_cache,
+    size_t page_stride, size_t head_stride, int token_stride, const int* __restrict__ block_table, int table_width,
+    const int* __restrict__ token_row, int page_size, int pages, int* status) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x, head = blockIdx.y;  // heads in the row's order: q heads, k heads, v heads
+    const int pos = positions[t];
+    T* row = x + (size_t)t * stride;
+    int page = -1, slot = 0;
+    if (k_cache && head >= q_heads) {
+        const int block = pos / page_size;
+        page = (pos >= 0 && block < table_width) ? block_table[(size_t)token_row[t] * table_width + block] : -1;
+        if (page < 0 || page >= pages) {
+            if (threadIdx.x == 0) atomicOr(status, HB_STATUS_BAD_PAGE);
+            page = -1;
+        }
+        slot = pos - block * page_size;
+    }
+    if (head < q_heads + kv_heads) {
+        const bool is_q = head < q_heads;
+        T* p = row + (size_t)head * head_dim;
+        const float* w = is_q ? q_norm : k_norm;
+        float inv = 1.f;
+        if (w) {
+            float sum = 0.f;
+            for (int i = threadIdx.x; i < head_dim; i += THREADS) {
+                const float v = to_float(p[i]);
+                sum = fmaf(v, v, sum);
+            }
+            inv = 1.0f / sqrtf(block_sum(sum, scratch) / (float)head_dim + eps);
+        }
+        T* dst = (is_q || !k_cache) ? p : (page >= 0 ? k_cache + (size_t)page * page_stride + (size_t)(head - q_heads) * head_stride + (size_t)slot * token_stride
+                                       : nullptr);
+        // pairs (2i, 2i+1): every thread handles whole pairs, so in-place writes never cross threads
+        for (int i = threadIdx.x; i < (head_dim + 1) / 2; i += THREADS) {
+            const int a = 2 * i, b = 2 * i + 1;
+            float u = to_float(p[a]) * inv * (w ? w[a] : 1.f);
+            float v = b < head_dim ? to_float(p[b]) * inv * (w ? w[b] : 1.f) : 0.f;
+            if (inv_freq && b < rot_dims) {
+                float s, c;
+                sincosf((float)pos * inv_freq[i], &s, &c);
+                const float ru = u * c - v * s, rv = v * c + u * s;
+                u = ru; v = rv;
+            }
+            if (dst) {
+                dst[a] = from_float<T>(u);
+                if (b < head_dim) dst[b] = from_float<T>(v);
+            }
+        }
+    } else {
+        const int vh = head - q_heads - kv_heads;
+        T* p = row + (size_t)(q_heads + kv_heads) * head_dim + (size_t)vh * v_dim;
+        const T* first = v_first ? v_first + (size_t)t * v_first_stride + (size_t)vh * v_dim : nullptr;
+        const float lam = first ? lambda[0] : 0.f;
+        T* dst = page >= 0 ? v_cache + (size_t)page * page_stride + (size_t)vh * head_stride + (size_t)slot * token_stride : nullptr;
+        for (int i = threadIdx.x; i < v_dim; i += THREADS) {
+            float v = to_float(p[i]);
+            if (first) v = (1.f - lam) * v + lam * to_float(first[i]);
+            if (dst) dst[i] = from_float<T>(v);
+        }
+    }
+}
+}  // namespace
+
+HB_EXPORT int hb_heads_prepare(void* x, int is_bf16, int tokens, int stride, int q_heads, int kv_heads, int head_dim, int v_dim,
+                               const float* q_norm, const float* k_norm, float eps, const float* inv_freq, int rot_dims,
+                               const int* positions, const void* v_first, int v_first_stride, const float* lambda, void* k_cache,
+                               void* v_cache, long long page_stride, long long head_stride, int token_stride, const int* block_table,
+                               int table_width, const int* token_row, int page_size, int pages, int with_values, int* status,
+                               cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (head_dim <= 0 || v_dim <= 0 || rot_dims < 0 || rot_dims > head_dim || (rot_dims & 1)) return HB_UNSUPPORTED_SIZE;
+    const int heads = q_heads + kv_heads + (with_values ? kv_heads : 0);
+    if (heads <= 0 || heads > 65535) return HB_UNSUPPORTED_SIZE;
+    const dim3 grid(tokens, heads);
+    if (is_bf16)
+        heads_prepare_kernel<<<grid, THREADS, 0, stream>>>((__nv_bfloat16*)x, stride, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, eps,
+                                                           inv_freq, rot_dims, positions, (const __nv_bfloat16*)v_first, v_first_stride, lambda,
+                                                           (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (size_t)page_stride, (size_t)head_stride,
+                                                           token_stride, block_table, table_width, token_row, page_size, pages, status);
+    else
+        heads_prepare_kernel<<<grid, THREADS, 0, stream>>>((float*)x, stride, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, eps, inv_freq,
+                                                           rot_dims, positions, (const float*)v_first, v_first_stride, lambda, (float*)k_cache,
+                                                           (float*)v_cache, (size_t)page_stride, (size_t)head_stride, token_stride, block_table,
+                                                           table_width, token_row, page_size, pages, status);
+    return launch_status();
+}

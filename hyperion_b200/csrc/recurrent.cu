@@ -1,0 +1,282 @@
+// Kernels of mixers that carry a state from token to token instead of a cache of keys: the short
+// causal convolution with its activation, the scan of a matrix-valued linear recurrence (the gated
+// delta rule and the state-space recurrence of Mamba-2 are two modes of one kernel), and the gated
+// group norm that follows it.  Everything here is float: inputs, state, decays, step sizes, gates
+// of the recurrence, unit norms and sums.  A request's state lives in its slot of a per-request
+// record (floats): first the matrices, then the convolution's last taps - 1 inputs.
+//
+// The scan.  Per head the state is a matrix S [n, e] (n: size of keys, e: size of values) and per
+// token, with a key k, a query q (both of size n), a value v (size e), a decay a and a step b:
+//     delta rule:   S <- a S;  u = b (v - S^T k);  S <- S + k u^T;  o = S^T q
+//     state space:  S <- a S + k (b v)^T;                           o = S^T q + D v
+// Column j of S (one value dimension) never meets another column, so the work is cut by columns:
+// eight lanes share a column, each holding n / 8 of its entries in registers (groups of four
+// consecutive entries, stored as S^T so that they are one 16-byte access), and a block of 128
+// threads walks 16 columns through the tokens of one request's row in order.  Sums over n are
+// taken in a fixed order (per lane, then a butterfly over the eight lanes), so a token's result
+// does not depend on how the request was cut into steps or on what else is in the batch.
+#include "common.cuh"
+
+namespace {
+constexpr int SCAN_THREADS = 128, SCAN_COLUMNS = 16;
+enum : int { MODE_DELTA = 0, MODE_STATE_SPACE = 1 };
+
+__device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
+__device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+
+// ---------------------------------------------------------------- causal convolution + SiLU
+// out[t, c] = silu(bias[c] + sum_j weight[c, taps-1-j] * x[t-j, c]) over the tokens of t's own request; inputs before
+// the row's first token come from the request's state (its last taps - 1 inputs, oldest first), which is zero for a new request.
+__global__ void causal_conv_silu_kernel(const float* __restrict__ x, int x_stride, int col0, int channels, const float* __restrict__ weight,
+                                        const float* __restrict__ bias, int taps, const float* __restrict__ state, size_t slot_stride,
+                                        int state_off, const int* __restrict__ slots, const int* __restrict__ token_row,
+                                        const int* __restrict__ row_start, float* __restrict__ out, size_t total) {
+    const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (index >= total) return;
+    const int t = (int)(index / channels), c = (int)(index - (size_t)t * channels);
+    const int r = token_row[t];
+    const int i = t - row_start[r];
+    const float* kept = state + (size_t)slots[r] * slot_stride + state_off;
+    float acc = bias ? bias[c] : 0.f;
+    for (int j = taps - 1; j >= 0; --j) {  // oldest input first
+        const float w = weight[(size_t)c * taps + taps - 1 - j];
+        const float v = (i - j >= 0) ? x[(size_t)(t - j) * x_stride + col0 + c] : kept[(size_t)(taps - 1 + i - j) * channels + c];
+        acc = fmaf(w, v, acc);
+    }
+    out[index] = silu_f(acc);
+}
+
+// The request's last taps - 1 inputs after this step's tokens (runs after the convolution has read the old ones).
+__global__ void conv_state_update_kernel(const float* __restrict__ x, int x_stride, int col0, int channels, int taps, float* __restrict__ state,
+                                         size_t slot_stride, int state_off, const int* __restrict__ slots, const int* __restrict__ row_start,
+                                         int rows) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x, r = blockIdx.y;
+    if (c >= channels || r >= rows) return;
+    const int first = row_start[r], n = row_start[r + 1] - first, keep = taps - 1;
+    float* kept = state + (size_t)slots[r] * slot_stride + state_off;
+    for (int s = 0; s < keep; ++s) {  // ascending: an old entry is read (at s + n > s) before it is overwritten
+        const int src = n - keep + s;
+        kept[(size_t)s * channels + c] = src >= 0 ? x[(size_t)(first + src) * x_stride + col0 + c] : kept[(size_t)(s + n) * channels + c];
+    }
+}
+
+// ---------------------------------------------------------------- the scan
+struct ScanArgs {
+    const float* conv;   // [tokens, conv_stride]: convolved and activated keys, queries and values
+    int conv_stride, k_off, q_off, v_off;
+    const float* proj;   // [tokens, proj_stride]: raw projections that give the decay and the step
+    int proj_stride, decay_off, step_off;
+    const float* a_log;  // [heads]
+    const float* dt_bias;  // [heads]
+    const float* skip;   // [heads] (state space: D)
+    float* state;
+    size_t slot_stride;
+    int state_off;
+    const int* slots;
+    const int* row_start;
+    float* out;          // [tokens, heads * e]
+    int heads, groups, n, n_padded, e;
+    float q_scale;
+};
+
+template <int NG, int MODE>
+__global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs a) {
+    const int row = blockIdx.z, head = blockIdx.y;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int l = lane & 7;
+    const int col = blockIdx.x * SCAN_COLUMNS + warp * 4 + (lane >> 3);
+    const bool col_ok = col < a.e;
+    const int t0 = a.row_start[row], t1 = a.row_start[row + 1];
+    const int group = head / (a.heads / a.groups);
+    float* mine = a.state + (size_t)a.slots[row] * a.slot_stride + a.state_off + ((size_t)head * a.e + (col_ok ? col : 0)) * a.n_padded;
+
+    float s[NG][4];
+#pragma unroll
+    for (int r = 0; r < NG; ++r) {
+        const int base = 32 * r + 4 * l;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (col_ok && base < a.n_padded) v = *reinterpret_cast<const float4*>(mine + base);
+        s[r][0] = v.x; s[r][1] = v.y; s[r][2] = v.z; s[r][3] = v.w;
+    }
+    const float a_rate = expf(a.a_log[head]);
+    const float bias = a.dt_bias[head];
+    const float skip = MODE == MODE_STATE_SPACE ? a.skip[head] : 0.f;
+
+    float kk[NG][4], qq[NG][4], vv = 0.f, decay_raw = 0.f, step_raw = 0.f;
+    auto fetch = [&](int t) {
+        const float* c = a.conv + (size_t)t * a.conv_stride;
+        const float* k = c + a.k_off + (size_t)group * a.n;
+        const float* q = c + a.q_off + (size_t)group * a.n;
+#pragma unroll
+        for (int r = 0; r < NG; ++r)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const int i = 32 * r + 4 * l + j;
+                kk[r][j] = i < a.n ? k[i] : 0.f;
+                qq[r][j] = i < a.n ? q[i] : 0.f;
+            }
+        vv = col_ok ? c[a.v_off + (size_t)head * a.e + col] : 0.f;
+        const float* p = a.proj + (size_t)t * a.proj_stride;
+        decay_raw = p[a.decay_off + head];
+        step_raw = MODE == MODE_DELTA ? p[a.step_off + head] : decay_raw;
+    };
+    if (t0 < t1) fetch(t0);
+    for (int t = t0; t < t1; ++t) {
+        float ck[NG][4], cq[NG][4];
+        const float cv = vv, c_decay = decay_raw, c_step = step_raw;
+#pragma unroll
+        for (int r = 0; r < NG; ++r)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { ck[r][j] = kk[r][j]; cq[r][j] = qq[r][j]; }
+        if (t + 1 < t1) fetch(t + 1);  // the next token's loads fly while this token is worked on
+
+        float decay, step;
+        if (MODE == MODE_DELTA) {
+            // keys and queries become unit vectors; the query also takes the scale
+            float sk = 0.f, sq = 0.f;
+#pragma unroll
+            for (int r = 0; r < NG; ++r)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { sk = fmaf(ck[r][j], ck[r][j], sk); sq = fmaf(cq[r][j], cq[r][j], sq); }
+#pragma unroll
+            for (int offset = 1; offset < 8; offset <<= 1) {
+                sk += __shfl_xor_sync(0xffffffffu, sk, offset);
+                sq += __shfl_xor_sync(0xffffffffu, sq, offset);
+            }
+            const float ik = 1.0f / sqrtf(sk + 1e-6f), iq = a.q_scale / sqrtf(sq + 1e-6f);
+#pragma unroll
+            for (int r = 0; r < NG; ++r)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { ck[r][j] *= ik; cq[r][j] *= iq; }
+            decay = expf(-a_rate * softplus_f(c_decay + bias));
+            step = 1.0f / (1.0f + expf(-c_step));
+        } else {
+            step = softplus_f(c_step + bias);
+            decay = expf(-a_rate * step);
+        }
+        float u;
+        if (MODE == MODE_DELTA) {
+            float dot = 0.f;
+#pragma unroll
+            for (int r = 0; r < NG; ++r)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) { s[r][j] *= decay; dot = fmaf(s[r][j], ck[r][j], dot); }
+#pragma unroll
+            for (int offset = 1; offset < 8; offset <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, offset);
+            u = step * (cv - dot);
+        } else {
+#pragma unroll
+            for (int r = 0; r < NG; ++r)
+#pragma unroll
+                for (int j = 0; j < 4; ++j) s[r][j] *= decay;
+            u = step * cv;
+        }
+        float o = 0.f;
+#pragma unroll
+        for (int r = 0; r < NG; ++r)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { s[r][j] = fmaf(ck[r][j], u, s[r][j]); o = fmaf(s[r][j], cq[r][j], o); }
+#pragma unroll
+        for (int offset = 1; offset < 8; offset <<= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
+        if (MODE == MODE_STATE_SPACE) o = fmaf(skip, cv, o);
+        if (l == 0 && col_ok) a.out[(size_t)t * a.heads * a.e + (size_t)head * a.e + col] = o;
+    }
+#pragma unroll
+    for (int r = 0; r < NG; ++r) {
+        const int base = 32 * r + 4 * l;
+        if (col_ok && base < a.n_padded) *reinterpret_cast<float4*>(mine + base) = make_float4(s[r][0], s[r][1], s[r][2], s[r][3]);
+    }
+}
+
+template <int MODE>
+int launch_scan(const ScanArgs& a, int rows, cudaStream_t stream) {
+    const dim3 grid((a.e + SCAN_COLUMNS - 1) / SCAN_COLUMNS, a.heads, rows);
+    if (a.n <= 32) state_scan_kernel<1, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
+    else if (a.n <= 64) state_scan_kernel<2, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
+    else if (a.n <= 128) state_scan_kernel<4, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
+    else state_scan_kernel<8, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------- gated group norm
+// One block per (token, group of `group` columns).  gate_first: v = y * silu(g), out = v / rms(v) * w; otherwise
+// out = y / rms(y) * w * silu(g).  The weight has `weight_len` entries and is indexed by column % weight_len (a weight
+// of one head's size is shared by all heads).
+template <typename TO>
+__global__ void gated_group_norm_kernel(const float* __restrict__ y, int y_stride, const float* __restrict__ gate, int gate_stride,
+                                        int gate_off, const float* __restrict__ weight, int weight_len, int group, int gate_first,
+                                        float eps, TO* __restrict__ out, int out_stride) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x, first = blockIdx.y * group;
+    const float* yrow = y + (size_t)t * y_stride + first;
+    const float* grow = gate + (size_t)t * gate_stride + gate_off + first;
+    float sum = 0.f;
+    for (int j = threadIdx.x; j < group; j += blockDim.x) {
+        float v = yrow[j];
+        if (gate_first) v *= silu_f(grow[j]);
+        sum = fmaf(v, v, sum);
+    }
+    const float inv = 1.0f / sqrtf(block_sum(sum, scratch) / (float)group + eps);
+    for (int j = threadIdx.x; j < group; j += blockDim.x) {
+        const float g = silu_f(grow[j]);
+        float v = yrow[j];
+        if (gate_first) v *= g;
+        v = v * inv * weight[(first + j) % weight_len];
+        if (!gate_first) v *= g;
+        out[(size_t)t * out_stride + first + j] = from_float<TO>(v);
+    }
+}
+}  // namespace
+
+HB_EXPORT int hb_causal_conv_silu(const float* x, int x_stride, int col0, int channels, const float* weight, const float* bias, int taps,
+                                  const float* state, long long slot_stride, int state_off, const int* slots, const int* token_row,
+                                  const int* row_start, float* out, int tokens, cudaStream_t stream) {
+    if (tokens <= 0 || channels <= 0) return 0;
+    if (taps < 1) return HB_BAD_ARGUMENT;
+    const size_t total = (size_t)tokens * channels;
+    causal_conv_silu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, x_stride, col0, channels, weight, bias, taps, state,
+                                                                                (size_t)slot_stride, state_off, slots, token_row, row_start, out, total);
+    return launch_status();
+}
+
+HB_EXPORT int hb_conv_state_update(const float* x, int x_stride, int col0, int channels, int taps, float* state, long long slot_stride,
+                                   int state_off, const int* slots, const int* row_start, int rows, cudaStream_t stream) {
+    if (rows <= 0 || channels <= 0 || taps <= 1) return 0;
+    if (rows > 65535) return HB_UNSUPPORTED_SIZE;
+    conv_state_update_kernel<<<dim3((channels + 127) / 128, rows), 128, 0, stream>>>(x, x_stride, col0, channels, taps, state, (size_t)slot_stride,
+                                                                                     state_off, slots, row_start, rows);
+    return launch_status();
+}
+
+// mode 0: gated delta rule (keys and queries made unit vectors, q times q_scale; decay = exp(-exp(a_log) softplus(proj[decay_off] + dt_bias)),
+// step = sigmoid(proj[step_off])).  mode 1: state space (step = softplus(proj[decay_off] + dt_bias), decay = exp(-exp(a_log) step), skip = D).
+// The state of (slot, head) is S^T [e, n_padded] at state + slot * slot_stride + state_off; n_padded, state_off and slot_stride are multiples of 4.
+HB_EXPORT int hb_state_scan(int mode, const float* conv, int conv_stride, int k_off, int q_off, int v_off, const float* proj, int proj_stride,
+                            int decay_off, int step_off, const float* a_log, const float* dt_bias, const float* skip, float* state,
+                            long long slot_stride, int state_off, const int* slots, const int* row_start, float* out, int rows, int heads,
+                            int groups, int n, int n_padded, int e, float q_scale, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (n <= 0 || n > 256 || e <= 0 || heads <= 0 || groups <= 0 || heads % groups || rows > 65535 || heads > 65535) return HB_UNSUPPORTED_SIZE;
+    if (n_padded < n || (n_padded & 3) || (state_off & 3) || (slot_stride & 3) || (((uintptr_t)state) & 15)) return HB_BAD_ARGUMENT;
+    ScanArgs a{conv, conv_stride, k_off, q_off, v_off, proj, proj_stride, decay_off, step_off, a_log, dt_bias, skip, state, (size_t)slot_stride,
+               state_off, slots, row_start, out, heads, groups, n, n_padded, e, q_scale};
+    if (mode == MODE_DELTA) return launch_scan<MODE_DELTA>(a, rows, stream);
+    if (mode == MODE_STATE_SPACE) return launch_scan<MODE_STATE_SPACE>(a, rows, stream);
+    return HB_BAD_ARGUMENT;
+}
+
+HB_EXPORT int hb_gated_group_norm(const float* y, int y_stride, const float* gate, int gate_stride, int gate_off, const float* weight,
+                                  int weight_len, int group, int groups, int gate_first, float eps, void* out, int out_is_bf16, int out_stride,
+                                  int tokens, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (group <= 0 || groups <= 0 || groups > 65535 || weight_len <= 0) return HB_UNSUPPORTED_SIZE;
+    const int threads = group >= 1024 ? 256 : (group >= 128 ? 128 : 64);
+    const dim3 grid(tokens, groups);
+    if (out_is_bf16)
+        gated_group_norm_kernel<<<grid, threads, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, gate_first, eps,
+                                                              (__nv_bfloat16*)out, out_stride);
+    else
+        gated_group_norm_kernel<<<grid, threads, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, gate_first, eps,
+                                                              (float*)out, out_stride);
+    return launch_status();
+}

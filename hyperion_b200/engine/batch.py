@@ -212,6 +212,9 @@ class StepContext:
     slots: torch.Tensor  # [R] int32
     extra: dict[str, torch.Tensor] = field(default_factory=dict)  # what planners of parts added
     host: dict[str, Any] = field(default_factory=dict)
+    # tensors of this step that one part leaves for another (a layer's values that later layers mix in, the stream in the
+    # activation type); made anew with every step and captured with it when the step becomes a graph
+    scratch: dict[Any, Any] = field(default_factory=dict)
 
     @property
     def n_rows(self) -> int:

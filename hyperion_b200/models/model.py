@@ -30,7 +30,7 @@ class DecoderModel:
         self.layers = []
         for layer in spec.layers:
             mixer = parts.make(parts.MIXERS, layer.mixer, self.build)
-            feed_forward = parts.make(parts.FEED_FORWARDS, layer.feed_forward, self.build)
+            feed_forward = parts.make(parts.FEED_FORWARDS, layer.feed_forward, self.build) if layer.feed_forward is not None else None
             norms = {name: parts.make(parts.NORMS, norm, self.build) for name, norm in layer.norms.items()}
             if layer.arrangement not in parts.ARRANGEMENTS:
                 raise KeyError(f"no arrangement {layer.arrangement!r} is registered")
@@ -47,7 +47,8 @@ class DecoderModel:
         yield self.spec.embedding.prefix, self.embedding
         for layer_spec, layer in zip(self.spec.layers, self.layers):
             yield layer_spec.mixer.prefix, layer.mixer
-            yield layer_spec.feed_forward.prefix, layer.feed_forward
+            if layer.feed_forward is not None:
+                yield layer_spec.feed_forward.prefix, layer.feed_forward
             for name, norm_spec in layer_spec.norms.items():
                 yield norm_spec.prefix, layer.norms[name]
         yield self.spec.final_norm.prefix, self.final_norm

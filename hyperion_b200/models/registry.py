@@ -1,6 +1,6 @@
 """The one registry from an architecture's name to its configuration type and its model.
 
-``config.json`` names the architecture in ``architectures``; the entry registered under that name
+``config.json`` names the architecture in ``architectures`` (a list) or ``architecture`` (one name); the entry registered under that name
 turns the parsed file into a typed configuration and the configuration into a
 :class:`~hyperion_b200.parts.spec.ModelSpec`.  The reference keeps the same kind of table from a
 model id to its compiler class, filled as a side effect of importing the architecture modules, and
@@ -35,6 +35,8 @@ def register_architecture(architecture: Architecture) -> None:
 
 def architecture_of(document: dict) -> Architecture:
     names = document.get("architectures")
+    if names is None and isinstance(document.get("architecture"), str):  # some designs name themselves with one string
+        names = [document["architecture"]]
     if not isinstance(names, list) or not names:
         raise ConfigError("architectures", f"must be a non-empty list, got {names!r}")
     for name in names:

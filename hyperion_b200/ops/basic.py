@@ -1,6 +1,8 @@
 """The row-wise operations and the 32-bit matrix product, as functions over torch tensors."""
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from .native import KernelError, check, f32, i32, is_bf16, library, ptr, require_cuda, stream_ptr
@@ -30,15 +32,15 @@ def raise_on_status(device: torch.device) -> None:
         raise KernelError(f"a kernel reported (status word {value:#x}): " + "; ".join(reasons))
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
-    """out[t] = float(table[ids[t]]); ids int32 on the device."""
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor | None = None, scale: float = 1.0) -> torch.Tensor:
+    """out[t] = float(table[ids[t]]) * scale; ids int32 on the device."""
     require_cuda(table, ids)
     tokens, (vocab, hidden) = ids.numel(), table.shape
     if out is None:
         out = torch.empty((tokens, hidden), dtype=torch.float32, device=table.device)
     lib = library("elementwise")
     check(lib.hb_embedding(ptr(table), i32(is_bf16(table)), ptr(ids), ptr(out), i32(tokens), i32(hidden), i32(vocab),
-                           ptr(status_word(table.device)), stream_ptr()), "embedding")
+                           f32(scale), ptr(status_word(table.device)), stream_ptr()), "embedding")
     return out
 
 
@@ -85,6 +87,32 @@ def add_rmsnorm(h: torch.Tensor, delta, weight: torch.Tensor, eps: float, out_dt
     check(lib.hb_add_rmsnorm(ptr(h), ptr(delta), i32(is_bf16(delta) if delta is not None else 0), ptr(weight), ptr(out),
                              i32(is_bf16(out)), ptr(rows), i32(n_rows), i32(hidden), f32(eps), write_h,
                              stream_ptr()), "add_rmsnorm")
+    return out
+
+
+def rmsnorm_add(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: float, copy_dtype: torch.dtype | None = None) -> torch.Tensor | None:
+    """h += y / sqrt(mean(y^2) + eps) * weight, row by row, in the float residual stream ``h``.  With ``copy_dtype``
+    bfloat16 the new rows are also returned in that type (the next sublayer's input); otherwise None."""
+    require_cuda(h, y, weight)
+    if h.dtype != torch.float32 or weight.dtype != torch.float32 or not h.is_contiguous() or not y.is_contiguous() or y.shape != h.shape:
+        raise KernelError("rmsnorm_add: a dense float32 stream, a float32 weight and a dense sublayer output of the stream's shape")
+    copy = None
+    if copy_dtype == torch.bfloat16:
+        if y.dtype != torch.bfloat16:
+            raise KernelError("rmsnorm_add: a bfloat16 copy is made beside a bfloat16 sublayer output")
+        copy = torch.empty_like(y)
+    check(library("elementwise").hb_rmsnorm_add(ptr(h), ptr(y), i32(is_bf16(y)), ptr(weight), ptr(copy), i32(h.shape[0]), i32(h.shape[1]),
+                                                f32(eps), stream_ptr()), "rmsnorm_add")
+    return copy
+
+
+def stream_copy(h: torch.Tensor) -> torch.Tensor:
+    """The float stream rounded to bfloat16."""
+    require_cuda(h)
+    if h.dtype != torch.float32 or not h.is_contiguous():
+        raise KernelError("stream_copy: a dense float32 stream")
+    out = torch.empty(h.shape, dtype=torch.bfloat16, device=h.device)
+    check(library("elementwise").hb_stream_copy(ptr(h), ptr(out), ctypes.c_longlong(h.numel()), stream_ptr()), "stream_copy")
     return out
 
 
@@ -158,6 +186,69 @@ def attention_generic(q: torch.Tensor, heads: int, cache: torch.Tensor, block_ta
                                    ptr(block_table), i32(block_table.shape[1]), ptr(token_row), ptr(positions), i32(tokens),
                                    i32(heads), i32(kv_heads), i32(head_dim), i32(page_size), i32(pages), f32(scale), i32(window or 0),
                                    ptr(status_word(q.device)), stream_ptr()), "attention_generic")
+    return out
+
+
+def paged_strides(cache: torch.Tensor, head_dim: int, v_dim: int) -> tuple[int, int, int, int]:
+    """(offset of the values, page stride, head stride, token stride), in elements, of a cache of keys and values in
+    either arrangement: [pages, 2, kv_heads, page, d] (keys and values of one size) or [pages, kv_heads, page, d + e]."""
+    if cache.dim() == 5:
+        pages, two, kv_heads, page_size, d = cache.shape
+        if two != 2 or d != head_dim or v_dim != head_dim or not cache.is_contiguous():
+            raise KernelError("a cache of [pages, 2, kv_heads, page, d] holds keys and values of one size d")
+        return kv_heads * page_size * d, 2 * kv_heads * page_size * d, page_size * d, d
+    pages, kv_heads, page_size, both = cache.shape
+    if both != head_dim + v_dim or not cache.is_contiguous():
+        raise KernelError("a cache of [pages, kv_heads, page, d + e] holds a key of d and a value of e per token")
+    return head_dim, kv_heads * page_size * both, page_size * both, both
+
+
+def heads_prepare_(x: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int, v_dim: int, positions: torch.Tensor, *,
+                   q_norm: torch.Tensor | None = None, k_norm: torch.Tensor | None = None, eps: float = 0.0,
+                   inv_freq: torch.Tensor | None = None, rot_dims: int = 0, v_first: torch.Tensor | None = None,
+                   mix: torch.Tensor | None = None, cache: torch.Tensor | None = None, block_table: torch.Tensor | None = None,
+                   token_row: torch.Tensor | None = None, page_size: int = 0) -> None:
+    """Rows ``x`` = [q | k | v]: query/key norm per head, rotation of interleaved pairs, value mixing with ``v_first``
+    (a view of another layer's value columns) by the scalar ``mix``, queries back in place, keys and values into
+    ``cache`` (either arrangement of :func:`paged_strides`); every step is optional."""
+    require_cuda(x, positions, q_norm, k_norm, inv_freq, v_first, mix, cache, block_table, token_row)
+    if x.stride(-1) != 1 or (v_first is not None and (v_first.stride(-1) != 1 or v_first.dtype != x.dtype)):
+        raise KernelError("heads_prepare: rows with unit inner stride")
+    for t in (q_norm, k_norm, inv_freq, mix):
+        if t is not None and t.dtype != torch.float32:
+            raise KernelError("heads_prepare: norm weights, frequencies and the mixing scalar are float32")
+    v_off = page_stride = head_stride = token_stride = pages = 0
+    if cache is not None:
+        if cache.dtype != x.dtype:
+            raise KernelError("heads_prepare: rows and cache must share their element type")
+        v_off, page_stride, head_stride, token_stride = paged_strides(cache, head_dim, v_dim)
+        pages = cache.shape[0]
+    element = x.element_size()
+    v_cache = ctypes.c_void_p(cache.data_ptr() + v_off * element) if cache is not None else ctypes.c_void_p(0)
+    check(library("heads_prepare").hb_heads_prepare(
+        ptr(x), i32(is_bf16(x)), i32(x.shape[0]), i32(x.stride(0)), i32(q_heads), i32(kv_heads), i32(head_dim), i32(v_dim), ptr(q_norm), ptr(k_norm),
+        f32(eps), ptr(inv_freq), i32(rot_dims if inv_freq is not None else 0), ptr(positions), ptr(v_first), i32(v_first.stride(0) if v_first is not None else 0),
+        ptr(mix), ptr(cache), v_cache, ctypes.c_longlong(page_stride), ctypes.c_longlong(head_stride), i32(token_stride), ptr(block_table),
+        i32(block_table.shape[1] if block_table is not None else 0), ptr(token_row), i32(page_size), i32(pages),
+        i32(1 if (cache is not None or v_first is not None) else 0), ptr(status_word(x.device)), stream_ptr()), "heads_prepare")
+
+
+def attention_general(q: torch.Tensor, heads: int, kv_heads: int, head_dim: int, v_dim: int, cache: torch.Tensor, block_table: torch.Tensor,
+                      token_row: torch.Tensor, positions: torch.Tensor, page_size: int, scale: float, softcap: float = 0.0, window: int = 0) -> torch.Tensor:
+    """Causal attention of every token over its request's pages with keys of ``head_dim`` and values of ``v_dim``, a smooth
+    cap on the scores (0 = none) and a window (0 = all keys); the cache in either arrangement of :func:`paged_strides`."""
+    require_cuda(q, cache, block_table, token_row, positions)
+    if q.dtype != cache.dtype or q.stride(-1) != 1:
+        raise KernelError("attention: queries and cache must share their element type")
+    v_off, page_stride, head_stride, token_stride = paged_strides(cache, head_dim, v_dim)
+    tokens = q.shape[0]
+    out = torch.empty((tokens, heads * v_dim), dtype=q.dtype, device=q.device)
+    v_cache = ctypes.c_void_p(cache.data_ptr() + v_off * cache.element_size())
+    check(library("attention_generic").hb_attention_general(
+        ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), i32(is_bf16(q)), ptr(cache), v_cache, ctypes.c_longlong(page_stride),
+        ctypes.c_longlong(head_stride), i32(token_stride), ptr(block_table), i32(block_table.shape[1]), ptr(token_row), ptr(positions), i32(tokens),
+        i32(heads), i32(kv_heads), i32(head_dim), i32(v_dim), i32(page_size), i32(cache.shape[0]), f32(scale), f32(softcap or 0.0), i32(window or 0),
+        ptr(status_word(q.device)), stream_ptr()), "attention_general")
     return out
 
 

@@ -1,0 +1,73 @@
+"""The operations of mixers that carry a state per request (``csrc/recurrent.cu``): the short causal convolution with its
+activation, the scan of a matrix-valued linear recurrence in its two modes, and the gated group norm.  All of them work in
+float32; a request's state is its slot of a float record [slots, floats] (the matrices first, the convolution's last
+inputs after them)."""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from .native import KernelError, check, f32, i32, is_bf16, library, ptr, require_cuda, stream_ptr
+
+MODE_DELTA, MODE_STATE_SPACE = 0, 1
+
+
+def _floats(*tensors) -> None:
+    for t in tensors:
+        if t is not None and (t.dtype != torch.float32 or t.stride(-1) != 1):
+            raise KernelError("the recurrent operations take float32 tensors with unit inner stride")
+
+
+def causal_conv_silu(x: torch.Tensor, col0: int, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor, state_off: int,
+                     slots: torch.Tensor, token_row: torch.Tensor, row_start: torch.Tensor) -> torch.Tensor:
+    """silu(causal convolution) of the columns ``col0 .. col0 + C`` of ``x`` [tokens, *] with ``weight`` [C, taps] (the last
+    column multiplies the current token); a row's earlier inputs come from its slot of ``state``."""
+    require_cuda(x, weight, bias, state, slots, token_row, row_start)
+    _floats(x, weight, bias, state)
+    channels, taps = weight.shape
+    out = torch.empty((x.shape[0], channels), dtype=torch.float32, device=x.device)
+    check(library("recurrent").hb_causal_conv_silu(ptr(x), i32(x.stride(0)), i32(col0), i32(channels), ptr(weight), ptr(bias), i32(taps), ptr(state),
+                                                   ctypes.c_longlong(state.stride(0)), i32(state_off), ptr(slots), ptr(token_row), ptr(row_start),
+                                                   ptr(out), i32(x.shape[0]), stream_ptr()), "causal_conv_silu")
+    return out
+
+
+def conv_state_update(x: torch.Tensor, col0: int, channels: int, taps: int, state: torch.Tensor, state_off: int, slots: torch.Tensor,
+                      row_start: torch.Tensor, rows: int) -> None:
+    """Every row's slot keeps its last ``taps - 1`` inputs (call after :func:`causal_conv_silu` of the same step)."""
+    require_cuda(x, state, slots, row_start)
+    _floats(x, state)
+    check(library("recurrent").hb_conv_state_update(ptr(x), i32(x.stride(0)), i32(col0), i32(channels), i32(taps), ptr(state),
+                                                    ctypes.c_longlong(state.stride(0)), i32(state_off), ptr(slots), ptr(row_start), i32(rows),
+                                                    stream_ptr()), "conv_state_update")
+
+
+def state_scan(mode: int, conv: torch.Tensor, k_off: int, q_off: int, v_off: int, proj: torch.Tensor, decay_off: int, step_off: int,
+               a_log: torch.Tensor, dt_bias: torch.Tensor, skip: torch.Tensor | None, state: torch.Tensor, state_off: int, slots: torch.Tensor,
+               row_start: torch.Tensor, rows: int, heads: int, groups: int, n: int, n_padded: int, e: int, q_scale: float = 1.0) -> torch.Tensor:
+    """Walk every row's tokens through the recurrence of ``mode`` from and into its slot of ``state``; returns [tokens, heads * e]."""
+    require_cuda(conv, proj, a_log, dt_bias, skip, state, slots, row_start)
+    _floats(conv, proj, a_log, dt_bias, skip, state)
+    out = torch.empty((conv.shape[0], heads * e), dtype=torch.float32, device=conv.device)
+    check(library("recurrent").hb_state_scan(i32(mode), ptr(conv), i32(conv.stride(0)), i32(k_off), i32(q_off), i32(v_off), ptr(proj), i32(proj.stride(0)),
+                                             i32(decay_off), i32(step_off), ptr(a_log), ptr(dt_bias), ptr(skip), ptr(state),
+                                             ctypes.c_longlong(state.stride(0)), i32(state_off), ptr(slots), ptr(row_start), ptr(out), i32(rows),
+                                             i32(heads), i32(groups), i32(n), i32(n_padded), i32(e), f32(q_scale), stream_ptr()), "state_scan")
+    return out
+
+
+def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, gate_off: int, weight: torch.Tensor, group: int, gate_first: bool, eps: float,
+                     out_dtype: torch.dtype) -> torch.Tensor:
+    """RMS norm of ``y`` [tokens, width] in groups of ``group`` columns, times ``weight`` (indexed by column modulo its length),
+    gated by silu of the columns ``gate_off ..`` of ``gate``: before the norm (``gate_first``) or after it."""
+    require_cuda(y, gate, weight)
+    _floats(y, gate, weight)
+    tokens, width = y.shape
+    if width % group:
+        raise KernelError(f"gated_group_norm: groups of {group} do not divide {width} columns")
+    out = torch.empty((tokens, width), dtype=out_dtype, device=y.device)
+    check(library("recurrent").hb_gated_group_norm(ptr(y), i32(y.stride(0)), ptr(gate), i32(gate.stride(0)), i32(gate_off), ptr(weight),
+                                                   i32(weight.numel()), i32(group), i32(width // group), i32(1 if gate_first else 0), f32(eps), ptr(out),
+                                                   i32(is_bf16(out)), i32(out.stride(0)), i32(tokens), stream_ptr()), "gated_group_norm")
+    return out

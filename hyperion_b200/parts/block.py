@@ -20,3 +20,35 @@ class PreNormBlock(Arrangement):
 
 
 register_arrangement("prenorm", PreNormBlock)
+
+
+class OutputNormBlock(Arrangement):
+    """The norm stands on each sublayer's output and the sublayers read the stream itself:
+    h <- h + norm_mixer(mixer(h)); h <- h + norm_ff(feed_forward(h)), the second line only when the layer has a
+    feed-forward.  Norm names: ``mixer_out`` and ``feed_forward_out``.  The stream stays float; in bfloat16 the
+    sublayers read a rounded copy of it, which the kernel that adds a sublayer's normalised output writes beside
+    the sum (``step.scratch`` hands it from layer to layer), so only a model's first layer makes one itself."""
+
+    COPY = "stream_in_activation_type"
+
+    def forward(self, h, delta, step, cache, own_cache):
+        from .. import ops
+
+        norm = self.norms["mixer_out"]
+        if delta is not None:  # a block before this one left an addition pending
+            h += (delta.tensor() if hasattr(delta, "tensor") else delta).to(h.dtype)
+            step.scratch.pop(self.COPY, None)
+        if norm.dtype == h.dtype:
+            x = h
+        else:
+            x = step.scratch.get(self.COPY)
+            if x is None:
+                x = ops.stream_copy(h)
+        x = norm.add_normed(h, self.mixer.forward(x, step, cache, own_cache))
+        if self.feed_forward is not None:
+            x = self.norms["feed_forward_out"].add_normed(h, self.feed_forward.forward(x, step))
+        step.scratch[self.COPY] = x
+        return h, None
+
+
+register_arrangement("output_norm", OutputNormBlock)

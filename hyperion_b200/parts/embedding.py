@@ -3,8 +3,9 @@
 h[t] = table[ids[t]] (helios/crates/helios-hal/kernels/elementwise.cu:13-19); logits = x head^T kept in
 float, where head is ``lm_head.weight`` or, with tied embeddings, the embedding table
 (helios/crates/helios-hal/src/backends/hopper_sm90/forward.rs:45-51, session.rs:844-848).
-Parameters: ``vocab_size``, ``hidden_size``; the head also ``tied`` (then it owns no tensor and is
-handed the embedding's table).
+Parameters: ``vocab_size``, ``hidden_size``, ``weight_name`` (the tensor's name after the prefix, ``weight``
+unless stated); the embedding also ``scale`` (the looked-up row is multiplied by it in float, 1 unless
+stated); the head also ``tied`` (then it owns no tensor and is handed the embedding's table).
 """
 from __future__ import annotations
 
@@ -22,18 +23,20 @@ class TokenEmbedding(Embedding):
         super().__init__(spec, build)
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
+        self.scale = float(spec.params.get("scale", 1.0))
+        self.weight_name = str(spec.params.get("weight_name", "weight"))
 
     def weights(self):
-        return {"weight": WeightSpec((self.vocab, self.hidden))}
+        return {self.weight_name: WeightSpec((self.vocab, self.hidden))}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.table = tensors["weight"].contiguous()
+        self.table = tensors[self.weight_name].contiguous()
 
     def kernel_modules(self):
         return [("elementwise", {})]
 
     def forward(self, token_ids):
-        return ops.embedding(self.table, token_ids)
+        return ops.embedding(self.table, token_ids, scale=self.scale)
 
     def shared_table(self):
         return self.table
@@ -45,14 +48,15 @@ class LinearHead(Head):
         self.vocab = int(spec.params["vocab_size"])
         self.hidden = int(spec.params["hidden_size"])
         self.tied = bool(spec.params.get("tied", False))
+        self.weight_name = str(spec.params.get("weight_name", "weight"))
         self.weight = None
 
     def weights(self):
-        return {} if self.tied else {"weight": WeightSpec((self.vocab, self.hidden))}
+        return {} if self.tied else {self.weight_name: WeightSpec((self.vocab, self.hidden))}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         if not self.tied:
-            self.weight = tensors["weight"].contiguous()
+            self.weight = tensors[self.weight_name].contiguous()
 
     def wants_shared_table(self) -> bool:
         return self.tied

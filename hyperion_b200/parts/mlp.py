@@ -5,7 +5,8 @@ matrix product (helios/crates/helios-hal/src/backends/hopper_sm90/backend.rs:95-
 silu(g) = g / (1 + exp(-g)) in float (kernels/elementwise.cu:28-37).  In bfloat16, when the intermediate size
 allows it, the rows alternate in runs of 128 gate rows and their 128 up rows, so that a prompt-sized
 product can apply SwiGLU in its epilogue (``ops.gated_linear``); otherwise the gate rows come first.
-Parameters: ``hidden_size``, ``intermediate_size``.
+Parameters: ``hidden_size``, ``intermediate_size``, ``names`` (the three tensors' names after the prefix as
+``{"gate": ..., "up": ..., "down": ...}``; the Hugging Face names unless stated).
 """
 from __future__ import annotations
 
@@ -28,13 +29,16 @@ class SwiGLU(FeedForward):
         super().__init__(spec, build)
         self.hidden = int(spec.params["hidden_size"])
         self.inter = int(spec.params["intermediate_size"])
+        names = dict(spec.params.get("names") or {})
+        self.gate_name, self.up_name = names.get("gate", "gate_proj.weight"), names.get("up", "up_proj.weight")
+        self.down_name = names.get("down", "down_proj.weight")
 
     def weights(self) -> dict[str, WeightSpec]:
-        return {"gate_proj.weight": WeightSpec((self.inter, self.hidden)), "up_proj.weight": WeightSpec((self.inter, self.hidden)),
-                "down_proj.weight": WeightSpec((self.hidden, self.inter))}
+        return {self.gate_name: WeightSpec((self.inter, self.hidden)), self.up_name: WeightSpec((self.inter, self.hidden)),
+                self.down_name: WeightSpec((self.hidden, self.inter))}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        pair = [tensors["gate_proj.weight"], tensors["up_proj.weight"]]
+        pair = [tensors[self.gate_name], tensors[self.up_name]]
         dtype = _common_dtype(pair)
         if dtype == torch.bfloat16 and self.inter % gemm.SWIGLU_BLOCK == 0:
             self.block = gemm.SWIGLU_BLOCK
@@ -42,7 +46,7 @@ class SwiGLU(FeedForward):
         else:
             self.block = None
             self.w_gate_up = torch.cat([t.to(dtype) for t in pair], dim=0).contiguous()
-        self.w_down = tensors["down_proj.weight"].contiguous()
+        self.w_down = tensors[self.down_name].contiguous()
 
     def kernel_modules(self):
         if self.dtype == torch.float32:

@@ -3,7 +3,11 @@
 y = x * rsqrt(mean(x^2) + eps) * weight, the weight multiplying after the normalisation
 (helios/crates/helios-hal/kernels/rmsnorm.cu:22-58); the fused form first adds the pending delta into
 the residual stream (rmsnorm.cu:66-122).  The stream, the sum of squares and the products are float;
-the result is rounded once to the activation type.  Parameters: ``hidden_size``, ``eps``.
+the result is rounded once to the activation type.  Parameters: ``hidden_size``, ``eps``, ``weight_name`` (the tensor's
+name after the prefix, ``weight`` unless stated).
+
+``add_normed`` is the other placement of the same norm: h <- h + norm(y), for blocks that normalise what a sublayer
+returns instead of what it reads.
 """
 from __future__ import annotations
 
@@ -21,19 +25,29 @@ class RMSNorm(Norm):
         super().__init__(spec, build)
         self.hidden = int(spec.params["hidden_size"])
         self.eps = float(spec.params["eps"])
+        self.weight_name = str(spec.params.get("weight_name", "weight"))
         self.weight: Optional[torch.Tensor] = None
 
     def weights(self) -> dict[str, WeightSpec]:
-        return {"weight": WeightSpec((self.hidden,), init="one_plus_normal")}
+        return {self.weight_name: WeightSpec((self.hidden,), init="one_plus_normal")}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].to(torch.float32).contiguous()
+        self.weight = tensors[self.weight_name].to(torch.float32).contiguous()
 
     def kernel_modules(self):
         return [("elementwise", {})]
 
     def forward(self, h, delta, rows=None):
         return ops.add_rmsnorm(h, delta, self.weight, self.eps, self.dtype, rows)
+
+    def add_normed(self, h, y):
+        """h <- h + norm(y) in the float stream; returns the new stream in the activation type (``h`` itself in float32)."""
+        if hasattr(y, "tensor"):
+            y = y.tensor()
+        if self.dtype == torch.float32:
+            ops.rmsnorm_add(h, y, self.weight, self.eps)
+            return h
+        return ops.rmsnorm_add(h, y, self.weight, self.eps, copy_dtype=self.dtype)
 
 
 register_norm("rmsnorm", RMSNorm)

@@ -1,0 +1,163 @@
+"""Two mixers that keep a matrix-valued state per request instead of a cache of keys: the gated delta rule and
+the state-space mixer of Mamba-2.  Both are one in-projection, a short causal convolution with SiLU over some of
+its columns, a scan of the recurrence over each request's new tokens (``csrc/recurrent.cu``), a gated RMS norm,
+and an out-projection.  The in-projection's result, the convolution, the recurrence with its decays, step
+sizes and unit norms, the state and the norm are float32 in both precisions; only the matrix products take
+bfloat16 operands in the bfloat16 mode.  A request's state is one float record (``RequestState``): the matrices
+of all heads, then the convolution's last taps - 1 inputs; it is zero when the request takes its slot.
+
+Gated delta rule (``delta_rule``), per head with key/query size n and value size e; the q/k head of head h is
+h // (heads / kv_heads):
+    q, k, v = silu(conv(W_q x)), silu(conv(W_k x)), silu(conv(W_v x));  q, k <- unit vectors (x / sqrt(|x|^2 + 1e-6)),  q <- q n^(-1/2)
+    beta = sigmoid(W_b x);  a = exp(-exp(A_log) softplus(W_a x + dt_bias))
+    S <- a S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q
+    y = o / rms(o) * norm * silu(W_g x)  per head, then W_o.
+Parameters: ``hidden_size``, ``heads``, ``kv_heads``, ``head_dim``, ``value_dim``, ``conv`` (taps), ``eps``.  Tensors (after the
+prefix): q, k, v, q.conv, k.conv, v.conv, b, a, A_log, dt_bias, g, norm, o.
+
+State space (``mamba2``), per head with state size n and value size e; the group of head h is h // (heads / groups):
+    [z | x | B | C | dt] = W_in x;  x, B, C <- silu(conv([x | B | C]) + conv.b);  dt <- softplus(dt + dt_bias)
+    S <- exp(-exp(A_log) dt) S + dt B x^T;  y = S^T C + D x
+    y <- y silu(z), RMS norm in ``norm_groups`` equal parts, times norm, then W_o.
+Parameters: ``hidden_size``, ``heads``, ``value_dim``, ``state``, ``groups``, ``norm_groups``, ``conv`` (taps), ``eps``.
+Tensors: in, conv, conv.b, dt_bias, A_log, D, norm, o.
+"""
+from __future__ import annotations
+
+from typing import Mapping
+
+import torch
+
+from .. import ops
+from ..ops import recurrent
+from .base import BuildContext, Mixer, RequestState, WeightSpec, register_mixer
+from .spec import PartSpec
+
+
+def _round_up(value: int, step: int) -> int:
+    return -(-value // step) * step
+
+
+class _ScanMixer(Mixer):
+    """What the two have in common: the record's layout and the sequence of kernels."""
+
+    mode: int
+    heads: int
+    groups: int
+    n: int  # size of keys and queries
+    e: int  # size of values
+    taps: int
+    conv_channels: int
+
+    def _finish_layout(self) -> None:
+        if self.n > 256:
+            raise ValueError(f"a state of {self.n} per column is above the scan kernel's limit of 256")
+        if self.heads % self.groups:
+            raise ValueError(f"{self.groups} groups do not divide {self.heads} heads")
+        self.n_padded = _round_up(self.n, 4)
+        self.conv_off = self.heads * self.e * self.n_padded  # a multiple of 4: the matrices come first
+        self.record = _round_up(self.conv_off + (self.taps - 1) * self.conv_channels, 4)
+
+    def cache_request(self):
+        return RequestState((self.record,), torch.float32)
+
+    def kernel_modules(self):
+        return [("recurrent", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
+
+    def _float(self, tensor: torch.Tensor) -> torch.Tensor:
+        return tensor.to(torch.float32).contiguous()
+
+
+class GatedDeltaRule(_ScanMixer):
+    mode = recurrent.MODE_DELTA
+
+    def __init__(self, spec: PartSpec, build: BuildContext):
+        super().__init__(spec, build)
+        p = spec.params
+        self.hidden, self.heads, self.groups = int(p["hidden_size"]), int(p["heads"]), int(p["kv_heads"])
+        self.n, self.e, self.taps, self.eps = int(p["head_dim"]), int(p["value_dim"]), int(p["conv"]), float(p["eps"])
+        self.qk_width, self.v_width = self.groups * self.n, self.heads * self.e
+        self.conv_channels = 2 * self.qk_width + self.v_width
+        # columns of the in-projection: [q | k | v | g | b | a]
+        self.gate_off = self.conv_channels
+        self.beta_off = self.gate_off + self.v_width
+        self.decay_off = self.beta_off + self.heads
+        self._finish_layout()
+
+    def weights(self) -> dict[str, WeightSpec]:
+        h, taps = self.hidden, self.taps
+        return {"q": WeightSpec((self.qk_width, h)), "k": WeightSpec((self.qk_width, h)), "v": WeightSpec((self.v_width, h)),
+                "q.conv": WeightSpec((self.qk_width, taps)), "k.conv": WeightSpec((self.qk_width, taps)), "v.conv": WeightSpec((self.v_width, taps)),
+                "b": WeightSpec((self.heads, h)), "a": WeightSpec((self.heads, h)), "A_log": WeightSpec((self.heads,)),
+                "dt_bias": WeightSpec((self.heads,)), "g": WeightSpec((self.v_width, h)), "norm": WeightSpec((self.e,), init="one_plus_normal"),
+                "o": WeightSpec((self.hidden, self.v_width))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        mats = [tensors[name] for name in ("q", "k", "v", "g", "b", "a")]
+        dtype = torch.float32 if any(m.dtype == torch.float32 for m in mats) else mats[0].dtype
+        self.w_in = torch.cat([m.to(dtype) for m in mats], dim=0).contiguous()
+        self.w_conv = torch.cat([self._float(tensors[name]) for name in ("q.conv", "k.conv", "v.conv")], dim=0).contiguous()
+        self.a_log, self.dt_bias = self._float(tensors["A_log"]), self._float(tensors["dt_bias"])
+        self.norm = self._float(tensors["norm"])
+        self.w_o = tensors["o"].contiguous()
+
+    def forward(self, x, step, cache, own_cache):
+        if cache is None or not own_cache:
+            raise ValueError("the delta rule keeps a state per request; the schedule gave it none")
+        proj = ops.linear(x, self.w_in, None, torch.float32)
+        state, slots, rows = cache.state, cache.slots, step.n_rows
+        conv = recurrent.causal_conv_silu(proj, 0, self.w_conv, None, state, self.conv_off, slots, step.token_row, step.row_start)
+        recurrent.conv_state_update(proj, 0, self.conv_channels, self.taps, state, self.conv_off, slots, step.row_start, rows)
+        o = recurrent.state_scan(self.mode, conv, self.qk_width, 0, 2 * self.qk_width, proj, self.decay_off, self.beta_off, self.a_log, self.dt_bias,
+                                 None, state, 0, slots, step.row_start, rows, self.heads, self.groups, self.n, self.n_padded, self.e,
+                                 q_scale=self.n ** -0.5)
+        y = recurrent.gated_group_norm(o, proj, self.gate_off, self.norm, self.e, False, self.eps, self.dtype)
+        return ops.linear(y, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
+
+
+class StateSpaceMixer(_ScanMixer):
+    mode = recurrent.MODE_STATE_SPACE
+
+    def __init__(self, spec: PartSpec, build: BuildContext):
+        super().__init__(spec, build)
+        p = spec.params
+        self.hidden, self.heads, self.groups = int(p["hidden_size"]), int(p["heads"]), int(p["groups"])
+        self.n, self.e, self.taps, self.eps = int(p["state"]), int(p["value_dim"]), int(p["conv"]), float(p["eps"])
+        self.norm_groups = int(p.get("norm_groups", 1))
+        self.inner = self.heads * self.e
+        if self.inner % self.norm_groups:
+            raise ValueError(f"{self.norm_groups} norm groups do not divide the inner width {self.inner}")
+        self.conv_channels = self.inner + 2 * self.groups * self.n
+        # columns of the in-projection: [z | x | B | C | dt]
+        self.conv_col0 = self.inner
+        self.dt_off = self.inner + self.conv_channels
+        self._finish_layout()
+
+    def weights(self) -> dict[str, WeightSpec]:
+        return {"in": WeightSpec((self.dt_off + self.heads, self.hidden)), "conv": WeightSpec((self.conv_channels, self.taps)),
+                "conv.b": WeightSpec((self.conv_channels,)), "dt_bias": WeightSpec((self.heads,)), "A_log": WeightSpec((self.heads,)),
+                "D": WeightSpec((self.heads,)), "norm": WeightSpec((self.inner,), init="one_plus_normal"), "o": WeightSpec((self.hidden, self.inner))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.w_in = tensors["in"].contiguous()
+        self.w_conv, self.b_conv = self._float(tensors["conv"]), self._float(tensors["conv.b"])
+        self.a_log, self.dt_bias, self.skip = self._float(tensors["A_log"]), self._float(tensors["dt_bias"]), self._float(tensors["D"])
+        self.norm = self._float(tensors["norm"])
+        self.w_o = tensors["o"].contiguous()
+
+    def forward(self, x, step, cache, own_cache):
+        if cache is None or not own_cache:
+            raise ValueError("the state-space mixer keeps a state per request; the schedule gave it none")
+        proj = ops.linear(x, self.w_in, None, torch.float32)
+        state, slots, rows = cache.state, cache.slots, step.n_rows
+        conv = recurrent.causal_conv_silu(proj, self.conv_col0, self.w_conv, self.b_conv, state, self.conv_off, slots, step.token_row, step.row_start)
+        recurrent.conv_state_update(proj, self.conv_col0, self.conv_channels, self.taps, state, self.conv_off, slots, step.row_start, rows)
+        bn = self.groups * self.n
+        y = recurrent.state_scan(self.mode, conv, self.inner, self.inner + bn, 0, proj, self.dt_off, self.dt_off, self.a_log, self.dt_bias, self.skip,
+                                 state, 0, slots, step.row_start, rows, self.heads, self.groups, self.n, self.n_padded, self.e)
+        y = recurrent.gated_group_norm(y, proj, 0, self.norm, self.inner // self.norm_groups, True, self.eps, self.dtype)
+        return ops.linear(y, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
+
+
+register_mixer("delta_rule", GatedDeltaRule)
+register_mixer("mamba2", StateSpaceMixer)

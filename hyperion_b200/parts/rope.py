@@ -51,3 +51,37 @@ class RotaryEncoding(PositionEncoding):
 
 
 register_position("rope", RotaryEncoding)
+
+
+class InterleavedRotaryEncoding(PositionEncoding):
+    """Rotary encoding of adjacent pairs: within the first ``dims`` dimensions of a head, dimension 2i is paired
+    with 2i + 1 and the pair (u, v) at position p becomes (u cos a - v sin a, v cos a + u sin a) with
+    a = p * base**(-2i/dims) / factor; dimensions from ``dims`` on pass unchanged.  ``factor`` is a linear
+    stretch of the positions (1 = none).  No table: the frequencies are computed once in float64 and kept in
+    float32, the angle and its sine and cosine are float32 on the device, so there is no limit on positions.
+    Parameters: ``dims``, ``base``, ``factor``."""
+
+    def __init__(self, spec: PartSpec, build: BuildContext):
+        super().__init__(spec, build)
+        self.dims = int(spec.params["dims"])
+        self.base = float(spec.params["base"])
+        self.factor = float(spec.params.get("factor", 1.0))
+        if self.dims % 2 or self.dims < 0:
+            raise ValueError(f"rotary encoding of pairs needs an even number of dimensions, got {self.dims}")
+        key = ("interleaved_frequencies", self.dims, self.base, self.factor, str(build.device))
+        if key not in build.shared:
+            i = torch.arange(self.dims // 2, dtype=torch.float64)
+            freq = torch.tensor(self.base, dtype=torch.float64) ** (-2.0 * i / max(1, self.dims)) / self.factor
+            build.shared[key] = freq.to(torch.float32).to(build.device)
+        self.inv_freq = build.shared[key]
+
+    def kernel_modules(self):
+        return [("heads_prepare", {})]
+
+    def apply_(self, x, heads, head_dim, positions):
+        if head_dim < self.dims:
+            raise ValueError(f"rotary encoding of {self.dims} dimensions, used with heads of {head_dim}")
+        ops.heads_prepare_(x, heads, 0, head_dim, head_dim, positions, inv_freq=self.inv_freq, rot_dims=self.dims)
+
+
+register_position("rope_interleaved", InterleavedRotaryEncoding)

@@ -26,9 +26,10 @@ class PartSpec:
 class LayerSpec:
     """One layer: an arrangement (how norms, mixer and feed-forward are wired) and its parts."""
 
+
     arrangement: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]  # None: the layer has a mixer only
     norms: Mapping[str, PartSpec]
 
 
