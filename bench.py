@@ -342,6 +342,148 @@ def reference_tables() -> int:
     return 0
 
 
+NUNIVIK_SIZES = {
+    # width, attention (heads, kv heads, head size, window), feed-forward, delta rule (heads, q/k heads, key size, value size),
+    # state space (heads, value size, state, groups); eight layers in the order A A D S A A D S, 32,000 tokens
+    "2k": {"width": 2048, "attention": (16, 4, 128, 1024), "ff": 8192, "delta": (16, 8, 128, 128), "mamba2": (64, 64, 128, 1)},
+    "4k": {"width": 4096, "attention": (32, 8, 128, 1024), "ff": 14336, "delta": (32, 16, 128, 128), "mamba2": (128, 64, 128, 8)},
+}
+
+
+def nunivik_document(size: dict, vocab: int = 32000) -> dict:
+    heads, kv_heads, dim, window = size["attention"]
+    attention = {"type": "attention", "mixer": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0,
+                                                "mask": {"size": window}, "rot": {"dims": dim, "base": 1e6, "scaling": {"factor": 1.0}}, "v_mix": True},
+                 "mlp": {"kind": "dense", "ff": size["ff"]}}
+    d = size["delta"]
+    delta = {"type": "delta", "mixer": {"heads": d[0], "kv_heads": d[1], "dim": d[2], "vdim": d[3], "conv": 4}, "mlp": None}
+    m = size["mamba2"]
+    mamba = {"type": "mamba2", "mixer": {"heads": m[0], "vdim": m[1], "state": m[2], "groups": m[3], "norm_groups": m[3], "conv": 4}, "mlp": None}
+    return {"architecture": "Nunivik", "vocab": vocab, "width": size["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "layers": [attention, attention, delta, mamba, attention, attention, delta, mamba]}
+
+
+def timed(fn, reps: int = 10, warmup: int = 3) -> float:
+    """Median milliseconds of ``fn`` by CUDA events, L2 flushed (a 256 MB buffer written) before every timed call."""
+    import torch
+
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    times = []
+    for r in range(warmup + reps):
+        flush.zero_()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        stop.record()
+        torch.cuda.synchronize()
+        if r >= warmup:
+            times.append(start.elapsed_time(stop))
+    return statistics.median(times)
+
+
+def nunivik_kernels(size: dict, measured: dict) -> dict:
+    """The design's own kernels alone at this size, a prompt of 2,048 tokens in one row and 8 rows of one decoded token: time, the bytes
+    each must move and, for the scans, the float32 operations, against the measured copy bandwidth (no float32 peak is measured: the
+    nominal 148 SMs x 128 lanes x 2 x 1.9 GHz = 72 TFLOP/s stands in)."""
+    import torch
+
+    from hyperion_b200 import ops
+    from hyperion_b200.ops import attention as fast, recurrent
+
+    dev = torch.device("cuda")
+    hbm = measured["hbm_gbs"] * 1e9
+    out: dict = {}
+    width = size["width"]
+
+    def rows_of(counts):
+        starts = [0]
+        for c in counts:
+            starts.append(starts[-1] + c)
+        token_row = torch.tensor([r for r, c in enumerate(counts) for _ in range(c)], dtype=torch.int32, device=dev)
+        return torch.tensor(starts, dtype=torch.int32, device=dev), token_row, torch.arange(len(counts), dtype=torch.int32, device=dev)
+
+    def report(name, ms, bytes_moved, flops=None):
+        entry = {"us": round(ms * 1e3, 2), "bytes": int(bytes_moved), "of_measured_bandwidth": round(bytes_moved / (ms / 1e3) / hbm, 3)}
+        if flops is not None:
+            entry["fp32_tflops"] = round(flops / (ms / 1e3) / 1e12, 2)
+        out[name] = entry
+
+    for shape, counts in (("prefill_2048", [PROMPT]), ("decode_8", [1] * 8)):
+        tokens = sum(counts)
+        row_start, token_row, slots = rows_of(counts)
+        h = torch.randn(tokens, width, device=dev)
+        y = torch.randn(tokens, width, device=dev).to(torch.bfloat16)
+        weight = torch.ones(width, device=dev)
+        report(f"rmsnorm_add/{shape}", timed(lambda: ops.rmsnorm_add(h, y, weight, 1e-6, copy_dtype=torch.bfloat16)), tokens * width * (4 + 4 + 2 + 2))
+        for kind, mode in (("delta", recurrent.MODE_DELTA), ("mamba2", recurrent.MODE_STATE_SPACE)):
+            if kind == "delta":
+                heads, groups, n, e = size["delta"]
+                channels = 2 * groups * n + heads * e
+                proj_width = channels + heads * e + 2 * heads
+                k_off, q_off, v_off, col0, decay_off, step_off, gate_off = groups * n, 0, 2 * groups * n, 0, channels + heads * e + heads, channels + heads * e, channels
+                group_width, gate_first = e, False
+            else:
+                heads, e, n, groups = size["mamba2"]
+                inner = heads * e
+                channels = inner + 2 * groups * n
+                proj_width = inner + channels + heads
+                k_off, q_off, v_off, col0, decay_off, step_off, gate_off = inner, inner + groups * n, 0, inner, inner + channels, inner + channels, 0
+                group_width, gate_first = inner // groups, True
+            taps = 4
+            record = -(-(heads * e * n + (taps - 1) * channels) // 4) * 4
+            state = torch.zeros(len(counts), record, device=dev)
+            proj = torch.randn(tokens, proj_width, device=dev) * 0.5
+            w_conv, a_log, dt_bias = torch.randn(channels, taps, device=dev) * 0.3, torch.zeros(heads, device=dev), torch.zeros(heads, device=dev)
+            skip = torch.ones(heads, device=dev)
+            conv = recurrent.causal_conv_silu(proj, col0, w_conv, None, state, heads * e * n, slots, token_row, row_start)
+            report(f"{kind}.conv/{shape}", timed(lambda: recurrent.causal_conv_silu(proj, col0, w_conv, None, state, heads * e * n, slots, token_row, row_start)),
+                   tokens * channels * 8)
+            scan = lambda: recurrent.state_scan(mode, conv, k_off, q_off, v_off, proj, decay_off, step_off, a_log, dt_bias, skip, state, 0, slots, row_start,
+                                                len(counts), heads, groups, n, n, e, q_scale=n ** -0.5)
+            moved = 4 * (tokens * (2 * groups * n + 2 * heads * e + 2 * heads) + 2 * len(counts) * heads * e * n)
+            report(f"{kind}.scan/{shape}", timed(scan), moved, flops=2.0 * (3 if kind == "delta" else 2) * tokens * heads * n * e)
+            o = scan()
+            norm_w = torch.ones(e if kind == "delta" else heads * e, device=dev)
+            report(f"{kind}.gated_norm/{shape}", timed(lambda: recurrent.gated_group_norm(o, proj, gate_off, norm_w, group_width, gate_first, 1e-6, torch.bfloat16)),
+                   tokens * heads * e * (4 + 4 + 2))
+    return out
+
+
+def nunivik_workload(args) -> int:
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 from a context of 2,048) of the Nunivik design at two sizes that
+    resemble real layers, beside the Qwen2 model of equal size (as many layers of the same width, heads and feed-forward), random weights."""
+    import torch
+
+    from hyperion_b200.api import Engine
+    from hyperion_b200.config import NunivikConfig, Qwen2Config
+
+    measured, kind = peaks()
+    for name, size in NUNIVIK_SIZES.items():
+        if args.size and name != args.size:
+            continue
+        heads, kv_heads, dim, _ = size["attention"]
+        arms = {
+            "nunivik": ("Nunivik", NunivikConfig.from_dict(nunivik_document(size))),
+            "qwen2": ("Qwen2ForCausalLM", Qwen2Config(num_hidden_layers=8, hidden_size=size["width"], intermediate_size=size["ff"], num_attention_heads=heads,
+                                                      num_key_value_heads=kv_heads, head_dim=dim, vocab_size=32000, max_position_embeddings=8192,
+                                                      rope_theta=1e6, rms_norm_eps=1e-6, tie_word_embeddings=False)),
+        }
+        line = {"workload": "nunivik", "size": name, "dtype": "bf16", "data": "synthetic: random weights and token ids", "layers": "A A D S A A D S",
+                "peaks": kind}
+        for arm, (architecture, config) in arms.items():
+            engine = Engine.from_random(architecture, config, seed=0, dtype="bfloat16", page_size=16, max_tokens=8 * (PROMPT + 256), max_requests=8)
+            prefill = time_prefill(engine)
+            decode = time_decode(engine, 8, 16, max(3, args.warmup), decode_tokens=max(3, args.warmup) + 160)
+            line[arm] = {"prefill_ms": round(prefill["ms"], 3), "prefill_tokens_per_s": round(PROMPT / prefill["ms"] * 1e3),
+                         "decode_ms_per_step": round(decode["ms_per_step"], 4), "decode_tokens_per_s": round(decode["tok_s"], 1),
+                         "decode_launches_per_step": round(decode["launches"] / decode["steps"], 1)}
+            del engine
+            torch.cuda.empty_cache()
+        line["kernels"] = nunivik_kernels(size, measured)
+        print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -354,15 +496,19 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 / 64 points, prefill and e2e")
     parser.add_argument("--only", default=None, choices=["prefill"], help="time one part alone (for profiling)")
-    parser.add_argument("--workload", default=None, choices=["mixed-1.5b", "batch-32b", "reference-tables"],
+    parser.add_argument("--workload", default=None, choices=["mixed-1.5b", "batch-32b", "reference-tables", "nunivik"],
                         help="one of the other workloads instead: 128 requests with prompts of 16..4096 tokens and 256 decoded tokens "
                              "each through generate() at the 1.5B shape; batch 16 with prompts of 4,096 and 512 decoded tokens at the 32B shape; "
-                             "or the reference's own published tables (decode by batch at context 512, prefill by length) at the 0.5B and 7B shapes")
+                             "or the reference's own published tables (decode by batch at context 512, prefill by length) at the 0.5B and 7B shapes; "
+                             "or the Nunivik design at two layer sizes beside the Qwen2 model of equal size, with its own kernels timed alone")
+    parser.add_argument("--size", default=None, choices=["2k", "4k"], help="with --workload nunivik: one of its sizes only")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
     if args.workload == "reference-tables":
         return reference_tables()
+    if args.workload == "nunivik":
+        return nunivik_workload(args)
     if args.workload:
         return other_workload(args.workload)
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:

@@ -81,6 +81,8 @@ def main(argv=None) -> int:
     _, config = read_model_config(Path(args.model))
     limit = getattr(config, "max_position_embeddings", None)
     max_seq_len = args.max_seq_len or limit
+    if max_seq_len is None:  # a design without a limit on positions: what these prompts can reach
+        max_seq_len = max(map(len, prompts)) + (args.max_tokens or args.default_max_tokens)
     if limit is not None and not 0 < max_seq_len <= limit:
         print(f"--max-seq-len {max_seq_len} is outside 1..={limit} (the model's max_seq_len): choose a value in that range", file=sys.stderr)
         return 2

@@ -121,6 +121,10 @@ class NunivikConfig:
                     raise ConfigError(path + "mlp.kind", f"{mlp.get('kind')!r} is not supported (only 'dense')")
                 ff = _positive_int(mlp, path + "mlp.", "ff")
             layers.append(NunivikLayer(kind, parsed, ff))
+        mixing = [(i, l.mixer.kv_heads * l.mixer.vdim) for i, l in enumerate(layers) if l.type == "attention" and l.mixer.v_mix]
+        for index, width in mixing[1:]:  # a later layer adds the first one's values to its own, head by head
+            if width != mixing[0][1]:
+                raise ConfigError(f"layers[{index}].mixer.v_mix", f"values of kv_heads * vdim = {width}, the first mixing layer has {mixing[0][1]}")
         eos = document.get("eos_token_id")
         eos_ids = tuple(eos if isinstance(eos, list) else [eos]) if eos is not None else ()
         return cls(vocab=_positive_int(document, "", "vocab"), width=_positive_int(document, "", "width"),

@@ -76,7 +76,7 @@ struct RowState {
 // thread's rows (hi < lo: nothing visible); `base`: position of the tile's key 0.
 template <int NT>
 __device__ __forceinline__ void process_keys(RowState& st, const bf16* qs, const bf16* ks, const bf16* vs, int key0, int base,
-                                             const int (&hi)[2], const int (&lo)[2], float scale_log2) {
+                                             const int (&hi)[2], const int (&lo)[2], float scale_log2, float cap_pre, float cap_post) {
     const int lane = threadIdx.x & 31;
     float s[NT][4];
 #pragma unroll
@@ -102,7 +102,7 @@ __device__ __forceinline__ void process_keys(RowState& st, const bf16* qs, const
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
             const int pos = base + key0 + n * 8 + (lane & 3) * 2 + (e & 1);
-            const float v = (pos <= hi[r] && pos >= lo[r]) ? s[n][e] * scale_log2 : -INFINITY;
+            const float v = (pos <= hi[r] && pos >= lo[r]) ? (cap_pre > 0.f ? capped_score_log2(s[n][e], cap_pre, cap_post) : s[n][e] * scale_log2) : -INFINITY;
             s[n][e] = v;
             mx[r] = fmaxf(mx[r], v);
         }
@@ -195,6 +195,7 @@ struct AttnArgs {
     int heads, kv_heads, page_size, pages, window;
     float scale_log2;                  // scale * log2(e)
     int* status;
+    float cap_pre, cap_post;  // scale / cap and cap * log2(e) of a smooth cap on the scores; cap_pre 0: none
 };
 
 // ---------------------------------------------------------------------------------- tile shape
@@ -255,7 +256,7 @@ __global__ void __launch_bounds__(THREADS) attention_tiles_kernel(AttnArgs a, co
         __syncthreads();
         const int base = start + it * BN;
         if (warp_has_rows && base <= warp_hi && base + BN - 1 >= warp_lo)
-            process_keys<BN / 8>(st, qs + warp * 16 * LDS, ks, ks + BN * LDS, 0, base, hi, lo, a.scale_log2);
+            process_keys<BN / 8>(st, qs + warp * 16 * LDS, ks, ks + BN * LDS, 0, base, hi, lo, a.scale_log2, a.cap_pre, a.cap_post);
         __syncthreads();
     }
 #pragma unroll
@@ -330,7 +331,7 @@ __global__ void __launch_bounds__(THREADS) attention_tokens_kernel(AttnArgs a, c
         __syncthreads();
         bf16* ks = kv + ((it - first) % TOKEN_STAGES) * 2 * BN * LDS;
         const int base = start + it * BN;
-        if (base + warp * 16 <= pos) process_keys<2>(st, qs, ks, ks + BN * LDS, warp * 16, base, hi, lo, a.scale_log2);
+        if (base + warp * 16 <= pos) process_keys<2>(st, qs, ks, ks + BN * LDS, warp * 16, base, hi, lo, a.scale_log2, a.cap_pre, a.cap_post);
         __syncthreads();
     }
     cp_async_wait<0>();
@@ -398,13 +399,14 @@ constexpr size_t TOKENS_SMEM = 16 * LDS * sizeof(bf16) + (TOKENS_KV_SMEM > TOKEN
 
 int fill_args(AttnArgs& a, const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
               int table_width, const int* token_row, const int* positions, int heads, int kv_heads, int head_dim, int page_size,
-              int pages, float scale, int window, int* status) {
+              int pages, float scale, float softcap, int window, int* status) {
     if (head_dim != D) return HB_UNSUPPORTED_SIZE;
     if (kv_heads <= 0 || heads % kv_heads || page_size <= 0 || q_stride % 8 || out_stride % 2) return HB_BAD_ARGUMENT;
     if (page_size & (page_size - 1)) return HB_UNSUPPORTED_SIZE;  // pages hold a power of two of tokens
     if (((uintptr_t)q | (uintptr_t)cache) & 15) return HB_BAD_ARGUMENT;
     a = AttnArgs{(const bf16*)q, q_stride, (bf16*)out, out_stride, (const bf16*)cache, block_table, table_width, token_row, positions,
-                 heads, kv_heads, page_size, pages, window, scale * 1.4426950408889634f, status};
+                 heads, kv_heads, page_size, pages, window, scale * 1.4426950408889634f, status,
+                 softcap > 0.f ? scale / softcap : 0.f, softcap * 1.4426950408889634f};
     return 0;
 }
 }  // namespace
@@ -417,14 +419,14 @@ HB_EXPORT int hb_attention_tile_tokens(int heads, int kv_heads) {
     return BM / (group < BM ? group : BM);
 }
 
-HB_EXPORT int hb_attention_tiles(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+HB_EXPORT int hb_attention_tiles_capped(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
                                  int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int heads,
-                                 int kv_heads, int head_dim, int page_size, int pages, float scale, int window, int* status,
+                                 int kv_heads, int head_dim, int page_size, int pages, float scale, float softcap, int window, int* status,
                                  cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     AttnArgs a;
     if (int code = fill_args(a, q, q_stride, out, out_stride, cache, block_table, table_width, token_row, positions, heads, kv_heads,
-                             head_dim, page_size, pages, scale, window, status)) return code;
+                             head_dim, page_size, pages, scale, softcap, window, status)) return code;
     const int group = heads / kv_heads, gc = group < BM ? group : BM, head_chunks = (group + gc - 1) / gc;
     if ((long long)kv_heads * head_chunks > 65535) return HB_UNSUPPORTED_SIZE;
     static bool configured = false;
@@ -437,19 +439,26 @@ HB_EXPORT int hb_attention_tiles(const void* q, int q_stride, void* out, int out
     return launch_status();
 }
 
+HB_EXPORT int hb_attention_tiles(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+                                 int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int heads,
+                                 int kv_heads, int head_dim, int page_size, int pages, float scale, int window, int* status,
+                                 cudaStream_t stream) {
+    return hb_attention_tiles_capped(q, q_stride, out, out_stride, cache, block_table, table_width, token_row, positions, tiles, n_tiles, heads, kv_heads, head_dim, page_size, pages, scale, 0.f, window, status, stream);
+}
+
 // Workspace floats needed by hb_attention_tokens for n_items tokens and `splits` splits.
 HB_EXPORT long long hb_attention_tokens_workspace(int n_items, int heads, int splits) {
     return splits <= 1 ? 0 : (long long)n_items * heads * splits * (D + 2);
 }
 
-HB_EXPORT int hb_attention_tokens(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+HB_EXPORT int hb_attention_tokens_capped(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
                                   int table_width, const int* token_row, const int* positions, const int* items, int n_items, int splits,
-                                  float* workspace, int heads, int kv_heads, int head_dim, int page_size, int pages, float scale,
+                                  float* workspace, int heads, int kv_heads, int head_dim, int page_size, int pages, float scale, float softcap,
                                   int window, int* status, cudaStream_t stream) {
     if (n_items <= 0) return 0;
     AttnArgs a;
     if (int code = fill_args(a, q, q_stride, out, out_stride, cache, block_table, table_width, token_row, positions, heads, kv_heads,
-                             head_dim, page_size, pages, scale, window, status)) return code;
+                             head_dim, page_size, pages, scale, softcap, window, status)) return code;
     const int group = heads / kv_heads, head_chunks = (group + 15) / 16;
     if (splits < 1 || splits > 65535 || (long long)kv_heads * head_chunks > 65535 || (splits > 1 && !workspace)) return HB_BAD_ARGUMENT;
     static bool configured = false;
@@ -465,4 +474,11 @@ HB_EXPORT int hb_attention_tokens(const void* q, int q_stride, void* out, int ou
     if (code || splits == 1) return code;
     attention_merge_kernel<<<dim3(n_items, heads), D < 64 ? 32 : (D < 128 ? 64 : 128), 0, stream>>>(items, ws_o, ws_ml, (bf16*)out, out_stride, heads, splits);
     return launch_status();
+}
+
+HB_EXPORT int hb_attention_tokens(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+                                  int table_width, const int* token_row, const int* positions, const int* items, int n_items, int splits,
+                                  float* workspace, int heads, int kv_heads, int head_dim, int page_size, int pages, float scale,
+                                  int window, int* status, cudaStream_t stream) {
+    return hb_attention_tokens_capped(q, q_stride, out, out_stride, cache, block_table, table_width, token_row, positions, items, n_items, splits, workspace, heads, kv_heads, head_dim, page_size, pages, scale, 0.f, window, status, stream);
 }

@@ -214,6 +214,7 @@ struct AttnArgs {
     float scale_log2;
     int* status;
     int wide_stores;  // rows of the output start on 32-byte boundaries
+    float cap_pre, cap_post;  // scale / cap and cap * log2(e) of a smooth cap on the scores (then scale_log2 is 1); cap_pre 0: none
 };
 
 // tiles[3*i] = first token (flat index), tiles[3*i+1] = token count, tiles[3*i+2] = batch row; virtual row v of a tile is
@@ -502,6 +503,10 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc_kernel(const __grid_c
                     float s[BN];
                     tmem_ld64(s_addr, s);
                     tmem_ld64(s_addr + 64, s + 64);
+                    if (a.cap_pre > 0.f) {  // capped scores come out in the exp2 domain; tanh keeps their order, so the maximum below stands
+#pragma unroll
+                        for (int i = 0; i < BN; ++i) s[i] = capped_score_log2(s[i], a.cap_pre, a.cap_post);
+                    }
                     const int tile_base = it.start + j * BN;
                     // one way for the whole warp: the masked walk only where some row of the warp needs it
                     const int last_visible = hi - tile_base, first_visible = lo - tile_base;  // among the tile's keys 0 .. BN - 1
@@ -636,9 +641,9 @@ constexpr size_t SMEM_BYTES = SMEM_USED > 120 * 1024 ? SMEM_USED : 120 * 1024;
 // 256 / min(group, 256) tokens.
 HB_EXPORT int hb_attention_tc_tile_rows() { return ROWS; }
 
-HB_EXPORT int hb_attention_tc_tiles(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+HB_EXPORT int hb_attention_tc_tiles_capped(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
                                     int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int n_tokens,
-                                    int heads, int kv_heads, int head_dim, int page_size, int pages, float scale, int window, int* status,
+                                    int heads, int kv_heads, int head_dim, int page_size, int pages, float scale, float softcap, int window, int* status,
                                     int* work, cudaStream_t stream) {
     (void)token_row;
     if (!work) return HB_BAD_ARGUMENT;
@@ -670,8 +675,8 @@ HB_EXPORT int hb_attention_tc_tiles(const void* q, int q_stride, void* out, int 
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return HB_BAD_ARGUMENT;
     AttnArgs a{(const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_width, positions,
-               heads, kv_heads, page_size, pages, window, scale * 1.4426950408889634f, status,
-               (((uintptr_t)out & 31) == 0 && out_stride % 16 == 0) ? 1 : 0};
+               heads, kv_heads, page_size, pages, window, softcap > 0.f ? 1.f : scale * 1.4426950408889634f, status,
+               (((uintptr_t)out & 31) == 0 && out_stride % 16 == 0) ? 1 : 0, softcap > 0.f ? scale / softcap : 0.f, softcap * 1.4426950408889634f};
     if ((long long)kv_heads * head_chunks > 65535) return HB_UNSUPPORTED_SIZE;
     static bool configured = false;
     if (!configured) {
@@ -688,4 +693,11 @@ HB_EXPORT int hb_attention_tc_tiles(const void* q, int q_stride, void* out, int 
     const int blocks = (int)(items < (long long)sms ? items : (long long)sms);
     return launch_after_previous(attention_tc_kernel, dim3(blocks), THREADS, SMEM_BYTES, stream, map, q_map, a, tiles, n_tiles, kv_heads * head_chunks, gc,
                                  head_chunks, work);
+}
+
+HB_EXPORT int hb_attention_tc_tiles(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+                                    int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int n_tokens,
+                                    int heads, int kv_heads, int head_dim, int page_size, int pages, float scale, int window, int* status,
+                                    int* work, cudaStream_t stream) {
+    return hb_attention_tc_tiles_capped(q, q_stride, out, out_stride, cache, block_table, table_width, token_row, positions, tiles, n_tiles, n_tokens, heads, kv_heads, head_dim, page_size, pages, scale, 0.f, window, status, work, stream);
 }

@@ -101,7 +101,7 @@ struct RowState {
 // One warp: 16 query rows (padded tile `qs`) against NT * 8 keys starting at key `key0` of the swizzled K / V tiles.
 template <int NT>
 __device__ __forceinline__ void process_keys(RowState& st, const bf16* qs, const bf16* ks, const bf16* vs, int key0, int base,
-                                             const int (&hi)[2], const int (&lo)[2], float scale_log2) {
+                                             const int (&hi)[2], const int (&lo)[2], float scale_log2, float cap_pre, float cap_post) {
     const int lane = threadIdx.x & 31, m = lane >> 3;
     float s[NT][4];
 #pragma unroll
@@ -125,7 +125,7 @@ __device__ __forceinline__ void process_keys(RowState& st, const bf16* qs, const
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
             const int pos = base + key0 + n * 8 + (lane & 3) * 2 + (e & 1);
-            const float v = (pos <= hi[r] && pos >= lo[r]) ? s[n][e] * scale_log2 : -INFINITY;
+            const float v = (pos <= hi[r] && pos >= lo[r]) ? (cap_pre > 0.f ? capped_score_log2(s[n][e], cap_pre, cap_post) : s[n][e] * scale_log2) : -INFINITY;
             s[n][e] = v;
             mx[r] = fmaxf(mx[r], v);
         }
@@ -183,6 +183,7 @@ struct AttnArgs {
     int heads, kv_heads, page_size, pages, window;
     float scale_log2;
     int* status;
+    float cap_pre, cap_post;  // scale / cap and cap * log2(e) of a smooth cap on the scores; cap_pre 0: none
 };
 
 __host__ __device__ constexpr int stages_for(bool tokens) { return D <= 64 ? 4 : (tokens && D <= 128 ? 3 : 2); }
@@ -361,10 +362,10 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
         const bf16* ks = reinterpret_cast<const bf16*>(ring + (size_t)s * STAGE_BYTES);
         const int base = start + it * BN;
         if (TOKENS) {
-            if (base + warp * 16 <= pos_last) process_keys<2>(st, qs, ks, ks + TILE_ELEMS, warp * 16, base, hi, lo, a.scale_log2);
+            if (base + warp * 16 <= pos_last) process_keys<2>(st, qs, ks, ks + TILE_ELEMS, warp * 16, base, hi, lo, a.scale_log2, a.cap_pre, a.cap_post);
         } else if (!TOKENS) {
             if (warp_has_rows && base <= warp_hi && base + BN - 1 >= warp_lo)
-                process_keys<BN / 8>(st, qs + warp * 16 * LDQ, ks, ks + TILE_ELEMS, 0, base, hi, lo, a.scale_log2);
+                process_keys<BN / 8>(st, qs + warp * 16 * LDQ, ks, ks + TILE_ELEMS, 0, base, hi, lo, a.scale_log2, a.cap_pre, a.cap_post);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
@@ -492,7 +493,7 @@ constexpr size_t smem_bytes() {
 // The cache layer as a matrix [pages * 2 * kv_heads * page_size, D] fetched in boxes of page_size rows x 64 columns.
 int prepare(CUtensorMap* map, AttnArgs& a, const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
             int table_width, const int* token_row, const int* positions, int heads, int kv_heads, int head_dim, int page_size, int pages,
-            float scale, int window, int* status) {
+            float scale, float softcap, int window, int* status) {
     if (head_dim != D) return HB_UNSUPPORTED_SIZE;
     if (kv_heads <= 0 || heads % kv_heads || q_stride % 8 || out_stride % 2) return HB_BAD_ARGUMENT;
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return HB_UNSUPPORTED_SIZE;
@@ -507,20 +508,21 @@ int prepare(CUtensorMap* map, AttnArgs& a, const void* q, int q_stride, void* ou
                CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return HB_BAD_ARGUMENT;
     a = AttnArgs{(const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_width, token_row, positions,
-                 heads, kv_heads, page_size, pages, window, scale * 1.4426950408889634f, status};
+                 heads, kv_heads, page_size, pages, window, scale * 1.4426950408889634f, status,
+                 softcap > 0.f ? scale / softcap : 0.f, softcap * 1.4426950408889634f};
     return 0;
 }
 }  // namespace
 
-HB_EXPORT int hb_attention_tma_tiles(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+HB_EXPORT int hb_attention_tma_tiles_capped(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
                                      int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int heads,
-                                     int kv_heads, int head_dim, int page_size, int pages, float scale, int window, int* status,
+                                     int kv_heads, int head_dim, int page_size, int pages, float scale, float softcap, int window, int* status,
                                      cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     CUtensorMap map;
     AttnArgs a;
     if (int code = prepare(&map, a, q, q_stride, out, out_stride, cache, block_table, table_width, token_row, positions, heads, kv_heads,
-                           head_dim, page_size, pages, scale, window, status)) return code;
+                           head_dim, page_size, pages, scale, softcap, window, status)) return code;
     const int group = heads / kv_heads, gc = group < 64 ? group : 64, head_chunks = (group + gc - 1) / gc;
     if ((long long)kv_heads * head_chunks > 65535) return HB_UNSUPPORTED_SIZE;
     static bool configured = false;
@@ -533,15 +535,22 @@ HB_EXPORT int hb_attention_tma_tiles(const void* q, int q_stride, void* out, int
                                  gc, head_chunks, 1, nullptr, nullptr);
 }
 
-HB_EXPORT int hb_attention_tma_tokens(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+HB_EXPORT int hb_attention_tma_tiles(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+                                     int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int heads,
+                                     int kv_heads, int head_dim, int page_size, int pages, float scale, int window, int* status,
+                                     cudaStream_t stream) {
+    return hb_attention_tma_tiles_capped(q, q_stride, out, out_stride, cache, block_table, table_width, token_row, positions, tiles, n_tiles, heads, kv_heads, head_dim, page_size, pages, scale, 0.f, window, status, stream);
+}
+
+HB_EXPORT int hb_attention_tma_tokens_capped(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
                                       int table_width, const int* token_row, const int* positions, const int* items, int n_items, int splits,
-                                      float* workspace, int heads, int kv_heads, int head_dim, int page_size, int pages, float scale,
+                                      float* workspace, int heads, int kv_heads, int head_dim, int page_size, int pages, float scale, float softcap,
                                       int window, int* status, cudaStream_t stream) {
     if (n_items <= 0) return 0;
     CUtensorMap map;
     AttnArgs a;
     if (int code = prepare(&map, a, q, q_stride, out, out_stride, cache, block_table, table_width, token_row, positions, heads, kv_heads,
-                           head_dim, page_size, pages, scale, window, status)) return code;
+                           head_dim, page_size, pages, scale, softcap, window, status)) return code;
     const int group = heads / kv_heads, head_chunks = (group + 15) / 16;
     if (splits < 1 || splits > 65535 || (long long)kv_heads * head_chunks > 65535 || (splits > 1 && !workspace)) return HB_BAD_ARGUMENT;
     static bool configured = false;
@@ -557,4 +566,11 @@ HB_EXPORT int hb_attention_tma_tokens(const void* q, int q_stride, void* out, in
     if (code || splits == 1) return code;
     return launch_after_previous(attention_merge_kernel, dim3(n_items, heads), D < 128 ? 64 : 128, 0, stream, items, (const float*)ws_o,
                                  (const float*)ws_ml, (bf16*)out, out_stride, heads, splits);
+}
+
+HB_EXPORT int hb_attention_tma_tokens(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+                                      int table_width, const int* token_row, const int* positions, const int* items, int n_items, int splits,
+                                      float* workspace, int heads, int kv_heads, int head_dim, int page_size, int pages, float scale,
+                                      int window, int* status, cudaStream_t stream) {
+    return hb_attention_tma_tokens_capped(q, q_stride, out, out_stride, cache, block_table, table_width, token_row, positions, items, n_items, splits, workspace, heads, kv_heads, head_dim, page_size, pages, scale, 0.f, window, status, stream);
 }

@@ -78,6 +78,15 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return best;
 }
 
+// A score capped smoothly, cap * tanh(raw * scale / cap), returned in the exp2 domain: `pre` = scale / cap, `post` = cap * log2(e).
+// tanh(z) = 1 - 2 / (1 + e^(2z)) with the hardware's exp2 and reciprocal: the absolute error of the capped score is some 1e-7 of
+// the cap, far below what the bfloat16 operands of the score carry.
+__device__ __forceinline__ float capped_score_log2(float raw, float pre, float post) {
+    float e;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(raw * pre * 2.8853900817779268f));
+    return post * (1.f - __fdividef(2.f, 1.f + e));
+}
+
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
 // ---------------------------------------------------------------- programmatic dependent launch

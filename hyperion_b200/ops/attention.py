@@ -35,8 +35,8 @@ def uses_tma(head_dim: int, page_size: int) -> bool:
 
 def _entry(head_dim: int, page_size: int, shape: str):
     if uses_tma(head_dim, page_size):
-        return getattr(library("attention_tma", HB_HEAD_DIM=head_dim), f"hb_attention_tma_{shape}")
-    return getattr(library("attention_bf16", HB_HEAD_DIM=head_dim), f"hb_attention_{shape}")
+        return getattr(library("attention_tma", HB_HEAD_DIM=head_dim), f"hb_attention_tma_{shape}_capped")
+    return getattr(library("attention_bf16", HB_HEAD_DIM=head_dim), f"hb_attention_{shape}_capped")
 
 
 def uses_tcgen05(head_dim: int, page_size: int) -> bool:
@@ -95,24 +95,27 @@ def _common(q, out, cache, block_table, token_row, positions):
         raise KernelError("attention (bfloat16): queries and cache must be dense bfloat16")
 
 
-def attention_tiles(q, heads, cache, block_table, token_row, positions, tiles, n_tiles, scale, window, out, tile_size: int = TILE_ROWS):
-    """``tile_size``: the virtual rows per tile the tiles were planned for (64, or 256 for the tcgen05 kernel)."""
+def attention_tiles(q, heads, cache, block_table, token_row, positions, tiles, n_tiles, scale, window, out, tile_size: int = TILE_ROWS,
+                    softcap: float = 0.0):
+    """``tile_size``: the virtual rows per tile the tiles were planned for (64, or 256 for the tcgen05 kernel).
+    ``softcap`` > 0: scores become cap * tanh(score / cap) before the softmax."""
     _common(q, out, cache, block_table, token_row, positions)
     pages, _, kv_heads, page_size, head_dim = cache.shape
     if uses_tcgen05(head_dim, page_size) and tile_size == TC_TILE_ROWS:
-        check(library("attention_tcgen05", HB_HEAD_DIM=head_dim).hb_attention_tc_tiles(
+        check(library("attention_tcgen05", HB_HEAD_DIM=head_dim).hb_attention_tc_tiles_capped(
             ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table), i32(block_table.shape[1]), ptr(token_row),
             ptr(positions), ptr(tiles), i32(n_tiles), i32(q.shape[0]), i32(heads), i32(kv_heads), i32(head_dim), i32(page_size), i32(pages),
-            f32(scale), i32(window or 0), ptr(status_word(q.device)), ptr(work_counters(q.device)), stream_ptr()), "attention_tiles")
+            f32(scale), f32(softcap or 0.0), i32(window or 0), ptr(status_word(q.device)), ptr(work_counters(q.device)), stream_ptr()), "attention_tiles")
         return
     entry = _entry(head_dim, page_size, "tiles")
     check(entry(ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table),
                                  i32(block_table.shape[1]), ptr(token_row), ptr(positions), ptr(tiles), i32(n_tiles), i32(heads),
-                                 i32(kv_heads), i32(head_dim), i32(page_size), i32(pages), f32(scale), i32(window or 0),
+                                 i32(kv_heads), i32(head_dim), i32(page_size), i32(pages), f32(scale), f32(softcap or 0.0), i32(window or 0),
                                  ptr(status_word(q.device)), stream_ptr()), "attention_tiles")
 
 
-def attention_tokens(q, heads, cache, block_table, token_row, positions, items, n_items, splits, scale, window, out, workspace=None):
+def attention_tokens(q, heads, cache, block_table, token_row, positions, items, n_items, splits, scale, window, out, workspace=None,
+                     softcap: float = 0.0):
     _common(q, out, cache, block_table, token_row, positions)
     pages, _, kv_heads, page_size, head_dim = cache.shape
     if splits > 1:
@@ -124,7 +127,7 @@ def attention_tokens(q, heads, cache, block_table, token_row, positions, items, 
     check(_entry(head_dim, page_size, "tokens")(ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table),
                                   i32(block_table.shape[1]), ptr(token_row), ptr(positions), ptr(items), i32(n_items), i32(splits),
                                   ptr(workspace), i32(heads), i32(kv_heads), i32(head_dim), i32(page_size), i32(pages), f32(scale),
-                                  i32(window or 0), ptr(status_word(q.device)), stream_ptr()), "attention_tokens")
+                                  f32(softcap or 0.0), i32(window or 0), ptr(status_word(q.device)), stream_ptr()), "attention_tokens")
     if splits > 1:
         from . import native
 

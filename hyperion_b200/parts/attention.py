@@ -39,6 +39,7 @@ class GroupedQueryAttention(Mixer):
         self.bias = bool(p.get("bias", False))
         self.scale = float(p.get("scale", self.head_dim ** -0.5))
         self.window = int(p.get("window", 0) or 0)
+        self.softcap = 0.0  # this part caps no scores; the kernels it shares with parts that do take the cap as an argument
         self.shares_kv = bool(p.get("shares_kv", False))
         if self.heads % self.kv_heads:
             raise ValueError(f"{self.kv_heads} key/value heads do not divide {self.heads} heads")
@@ -138,13 +139,13 @@ class GroupedQueryAttention(Mixer):
         return max(row.position + row.count for row in rows if row.count <= fast_attention.TOKEN_SHAPE_MAX)
 
     def _attend_fast(self, qkv, step, cache):
-        out = torch.empty((step.n_tokens, self.q_width), dtype=self.dtype, device=qkv.device)
+        out = torch.empty((step.n_tokens, self.heads * self.head_dim), dtype=self.dtype, device=qkv.device)
         size = fast_attention.tile_rows(self.head_dim, step.host.get("page_size"))
         key = f"attn_tiles_{fast_attention.tile_tokens(self.heads, self.kv_heads, size)}"
         n_tiles, n_items = step.host.get(key, 0), step.host.get("attn_items", 0)
         if n_tiles:
             fast_attention.attention_tiles(qkv, self.heads, cache.kv, cache.block_table, step.token_row, step.positions,
-                                           step.extra[key], n_tiles, self.scale, self.window, out, tile_size=size)
+                                           step.extra[key], n_tiles, self.scale, self.window, out, tile_size=size, softcap=self.softcap)
         if n_items:
             # a step replayed from a CUDA graph fixes its launch shape for every context its tables can hold
             longest = step.host.get("context_cap") or self._longest_short_row(step.rows)
@@ -152,7 +153,7 @@ class GroupedQueryAttention(Mixer):
                 longest = min(longest, self.window + fast_attention.KEY_TILE)
             splits = fast_attention.choose_splits(n_items, self.heads, self.kv_heads, longest)
             fast_attention.attention_tokens(qkv, self.heads, cache.kv, cache.block_table, step.token_row, step.positions,
-                                            step.extra["attn_items"], n_items, splits, self.scale, self.window, out)
+                                            step.extra["attn_items"], n_items, splits, self.scale, self.window, out, softcap=self.softcap)
         return out
 
 

@@ -17,8 +17,11 @@ layer's own scalar exists in the checkpoint and is not used.
 Parameters: ``hidden_size``, ``heads``, ``kv_heads``, ``head_dim``, ``value_dim`` (``head_dim`` unless stated),
 ``scale``, ``softcap`` (0 = none), ``window`` (0 = all keys), ``qk_norm`` (bool), ``eps``, ``position`` (a PartSpec
 or None), ``v_mix`` (a key, or None), ``names`` (tensor names after the prefix: q, k, v, o, q_norm, k_norm, v_mix).
-Keys and values of one size lie in pages of [2, kv_heads, page, d] like every other attention's; of two sizes in
-pages of [kv_heads, page, d + e].
+Keys and values of one size lie in pages of [2, kv_heads, page, d] like every other attention's, and in bfloat16 with
+head sizes the tensor-core kernels take they are read by those kernels (``GroupedQueryAttention``'s own: tcgen05 tiles
+for prompt portions, the TMA-fed split-key kernel for decoded tokens), which take the cap and the window as
+arguments; of two sizes they lie in pages of [kv_heads, page, d + e] and are read by the general kernel, as is
+everything in float32.
 """
 from __future__ import annotations
 
@@ -27,6 +30,8 @@ from typing import Mapping
 import torch
 
 from .. import ops
+from ..ops import attention as fast_attention
+from .attention import GroupedQueryAttention
 from .base import POSITIONS, BuildContext, Mixer, PagedKV, PagedTokens, WeightSpec, make, register_mixer
 from .spec import PartSpec
 
@@ -38,10 +43,13 @@ def _common_dtype(tensors) -> torch.dtype:
     return torch.float32 if any(t.dtype == torch.float32 for t in tensors) else tensors[0].dtype
 
 
-class CappedAttention(Mixer):
+class CappedAttention(GroupedQueryAttention):
+    """Shares the planning and the launches of the tensor-core path with its base; everything else is its own."""
+
     def __init__(self, spec: PartSpec, build: BuildContext):
-        super().__init__(spec, build)
+        Mixer.__init__(self, spec, build)
         p = spec.params
+        self.bias, self.shares_kv = False, False
         self.hidden = int(p["hidden_size"])
         self.heads = int(p["heads"])
         self.kv_heads = int(p["kv_heads"])
@@ -64,6 +72,7 @@ class CappedAttention(Mixer):
         self.q_width = self.heads * self.head_dim
         self.k_width = self.kv_heads * self.head_dim
         self.v_width = self.kv_heads * self.value_dim
+        self.fast = self.dtype == torch.bfloat16 and self.value_dim == self.head_dim and fast_attention.supported(self.head_dim)
 
     def weights(self) -> dict[str, WeightSpec]:
         n = self.names
@@ -92,7 +101,15 @@ class CappedAttention(Mixer):
         return PagedTokens((self.kv_heads,), (self.head_dim + self.value_dim,), self.window)
 
     def kernel_modules(self):
-        return [("heads_prepare", {}), ("attention_generic", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
+        modules = [("heads_prepare", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
+        if not self.fast:
+            return modules + [("attention_generic", {})]
+        modules.append(("attention_bf16", {"HB_HEAD_DIM": self.head_dim}))  # which is launched depends on the page size of the cache
+        if self.head_dim % 64 == 0:
+            modules.append(("attention_tma", {"HB_HEAD_DIM": self.head_dim}))
+        if self.head_dim in (64, 128):
+            modules.append(("attention_tcgen05", {"HB_HEAD_DIM": self.head_dim}))
+        return modules
 
     def forward(self, x, step, cache, own_cache):
         if cache is None or not own_cache:
@@ -111,8 +128,11 @@ class CappedAttention(Mixer):
                            rot_dims=self.position.dims if self.position is not None else 0, v_first=v_first,
                            mix=self.mix if v_first is not None else None, cache=cache.kv, block_table=cache.block_table,
                            token_row=step.token_row, page_size=cache.page_size)
-        attn = ops.attention_general(qkv, self.heads, self.kv_heads, self.head_dim, self.value_dim, cache.kv, cache.block_table, step.token_row,
-                                     step.positions, cache.page_size, self.scale, self.softcap, self.window)
+        if self.fast:
+            attn = self._attend_fast(qkv, step, cache)
+        else:
+            attn = ops.attention_general(qkv, self.heads, self.kv_heads, self.head_dim, self.value_dim, cache.kv, cache.block_table, step.token_row,
+                                         step.positions, cache.page_size, self.scale, self.softcap, self.window)
         return ops.linear(attn, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
 
 
