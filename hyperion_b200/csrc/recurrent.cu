@@ -13,12 +13,13 @@
 // eight lanes share a column, each holding n / 8 of its entries in registers (groups of four
 // consecutive entries, stored as S^T so that they are one 16-byte access), and a block of 128
 // threads walks 16 columns through the tokens of one request's row in order.  Sums over n are
-// taken in a fixed order (per lane, then a butterfly over the eight lanes), so a token's result
-// does not depend on how the request was cut into steps or on what else is in the batch.
+// taken in a fixed order (per lane in four chains, then a butterfly over the eight lanes), so a
+// token's result does not depend on how the request was cut into steps or on what else is in
+// the batch.
 #include "common.cuh"
 
 namespace {
-constexpr int SCAN_THREADS = 128, SCAN_COLUMNS = 16;
+constexpr int SCAN_THREADS = 128;
 enum : int { MODE_DELTA = 0, MODE_STATE_SPACE = 1 };
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
@@ -30,10 +31,9 @@ __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log
 __global__ void causal_conv_silu_kernel(const float* __restrict__ x, int x_stride, int col0, int channels, const float* __restrict__ weight,
                                         const float* __restrict__ bias, int taps, const float* __restrict__ state, size_t slot_stride,
                                         int state_off, const int* __restrict__ slots, const int* __restrict__ token_row,
-                                        const int* __restrict__ row_start, float* __restrict__ out, size_t total) {
-    const size_t index = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (index >= total) return;
-    const int t = (int)(index / channels), c = (int)(index - (size_t)t * channels);
+                                        const int* __restrict__ row_start, float* __restrict__ out, int first_token) {
+    const int t = first_token + blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;  // a block: one token, consecutive channels
+    if (c >= channels) return;
     const int r = token_row[t];
     const int i = t - row_start[r];
     const float* kept = state + (size_t)slots[r] * slot_stride + state_off;
@@ -43,7 +43,7 @@ __global__ void causal_conv_silu_kernel(const float* __restrict__ x, int x_strid
         const float v = (i - j >= 0) ? x[(size_t)(t - j) * x_stride + col0 + c] : kept[(size_t)(taps - 1 + i - j) * channels + c];
         acc = fmaf(w, v, acc);
     }
-    out[index] = silu_f(acc);
+    out[(size_t)t * channels + c] = silu_f(acc);
 }
 
 // The request's last taps - 1 inputs after this step's tokens (runs after the convolution has read the old ones).
@@ -79,12 +79,21 @@ struct ScanArgs {
     float q_scale;
 };
 
-template <int NG, int MODE>
+template <int NG, int LPC, int MODE>  // NG groups of four entries per lane, LPC lanes per column: n <= NG * 4 * LPC
 __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs a) {
+    // The tokens of the row pass through shared memory in chunks: while the block walks one chunk, every warp holds the next
+    // chunk's share (every fourth token) in registers, already asked from memory; after the walk it turns them into what the
+    // walk needs (unit keys and queries, decay, step) and writes them to the other buffer.  Nothing of that preparation lies on
+    // the chain from one token's state to the next.
+    constexpr int NP = NG * 4 * LPC, NPR = NP / 32, COLUMNS = 128 / LPC, CT = NP >= 256 ? 8 : 16, PER_WARP = CT / 4;
+    __shared__ __align__(16) float sk[2][CT][NP];
+    __shared__ __align__(16) float sq[2][CT][NP];
+    __shared__ float sv[2][CT][COLUMNS], sdecay[2][CT], sstep[2][CT];
+
     const int row = blockIdx.z, head = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int l = lane & 7;
-    const int col = blockIdx.x * SCAN_COLUMNS + warp * 4 + (lane >> 3);
+    const int l = lane % LPC, cw = warp * (32 / LPC) + lane / LPC;
+    const int col0 = blockIdx.x * COLUMNS, col = col0 + cw;
     const bool col_ok = col < a.e;
     const int t0 = a.row_start[row], t1 = a.row_start[row + 1];
     const int group = head / (a.heads / a.groups);
@@ -93,7 +102,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
     float s[NG][4];
 #pragma unroll
     for (int r = 0; r < NG; ++r) {
-        const int base = 32 * r + 4 * l;
+        const int base = 4 * (LPC * r + l);
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
         if (col_ok && base < a.n_padded) v = *reinterpret_cast<const float4*>(mine + base);
         s[r][0] = v.x; s[r][1] = v.y; s[r][2] = v.z; s[r][3] = v.w;
@@ -102,99 +111,130 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
     const float bias = a.dt_bias[head];
     const float skip = MODE == MODE_STATE_SPACE ? a.skip[head] : 0.f;
 
-    float kk[NG][4], qq[NG][4], vv = 0.f, decay_raw = 0.f, step_raw = 0.f;
-    auto fetch = [&](int t) {
-        const float* c = a.conv + (size_t)t * a.conv_stride;
-        const float* k = c + a.k_off + (size_t)group * a.n;
-        const float* q = c + a.q_off + (size_t)group * a.n;
+    float pk[PER_WARP][NPR], pq[PER_WARP][NPR], pv[PER_WARP], pdecay[PER_WARP], pstep[PER_WARP];
+    auto prefetch = [&](int first) {
 #pragma unroll
-        for (int r = 0; r < NG; ++r)
+        for (int i = 0; i < PER_WARP; ++i) {
+            const int t = first + warp + 4 * i;
+            const bool live = t < t1;
+            const float* c = a.conv + (size_t)(live ? t : t0) * a.conv_stride;
+            const float* k = c + a.k_off + (size_t)group * a.n;
+            const float* q = c + a.q_off + (size_t)group * a.n;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int i = 32 * r + 4 * l + j;
-                kk[r][j] = i < a.n ? k[i] : 0.f;
-                qq[r][j] = i < a.n ? q[i] : 0.f;
+            for (int r = 0; r < NPR; ++r) {
+                const int index = lane + 32 * r;
+                pk[i][r] = (live && index < a.n) ? k[index] : 0.f;
+                pq[i][r] = (live && index < a.n) ? q[index] : 0.f;
             }
-        vv = col_ok ? c[a.v_off + (size_t)head * a.e + col] : 0.f;
-        const float* p = a.proj + (size_t)t * a.proj_stride;
-        decay_raw = p[a.decay_off + head];
-        step_raw = MODE == MODE_DELTA ? p[a.step_off + head] : decay_raw;
+            pv[i] = (live && lane < COLUMNS && col0 + lane < a.e) ? c[a.v_off + (size_t)head * a.e + col0 + lane] : 0.f;
+            const float* p = a.proj + (size_t)(live ? t : t0) * a.proj_stride;
+            pdecay[i] = live ? p[a.decay_off + head] : 0.f;
+            pstep[i] = (live && MODE == MODE_DELTA) ? p[a.step_off + head] : 0.f;
+        }
     };
-    if (t0 < t1) fetch(t0);
-    for (int t = t0; t < t1; ++t) {
-        float ck[NG][4], cq[NG][4];
-        const float cv = vv, c_decay = decay_raw, c_step = step_raw;
+    auto publish = [&](int buffer) {
 #pragma unroll
-        for (int r = 0; r < NG; ++r)
+        for (int i = 0; i < PER_WARP; ++i) {
+            const int j = warp + 4 * i;
+            float ik = 1.f, iq = 1.f;
+            if (MODE == MODE_DELTA) {  // keys and queries become unit vectors; the query also takes the scale
+                float sum_k = 0.f, sum_q = 0.f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) { ck[r][j] = kk[r][j]; cq[r][j] = qq[r][j]; }
-        if (t + 1 < t1) fetch(t + 1);  // the next token's loads fly while this token is worked on
-
-        float decay, step;
-        if (MODE == MODE_DELTA) {
-            // keys and queries become unit vectors; the query also takes the scale
-            float sk = 0.f, sq = 0.f;
-#pragma unroll
-            for (int r = 0; r < NG; ++r)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) { sk = fmaf(ck[r][j], ck[r][j], sk); sq = fmaf(cq[r][j], cq[r][j], sq); }
-#pragma unroll
-            for (int offset = 1; offset < 8; offset <<= 1) {
-                sk += __shfl_xor_sync(0xffffffffu, sk, offset);
-                sq += __shfl_xor_sync(0xffffffffu, sq, offset);
+                for (int r = 0; r < NPR; ++r) { sum_k = fmaf(pk[i][r], pk[i][r], sum_k); sum_q = fmaf(pq[i][r], pq[i][r], sum_q); }
+                ik = 1.0f / sqrtf(warp_sum(sum_k) + 1e-6f);
+                iq = a.q_scale / sqrtf(warp_sum(sum_q) + 1e-6f);
             }
-            const float ik = 1.0f / sqrtf(sk + 1e-6f), iq = a.q_scale / sqrtf(sq + 1e-6f);
 #pragma unroll
-            for (int r = 0; r < NG; ++r)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) { ck[r][j] *= ik; cq[r][j] *= iq; }
-            decay = expf(-a_rate * softplus_f(c_decay + bias));
-            step = 1.0f / (1.0f + expf(-c_step));
-        } else {
-            step = softplus_f(c_step + bias);
-            decay = expf(-a_rate * step);
+            for (int r = 0; r < NPR; ++r) {
+                sk[buffer][j][lane + 32 * r] = pk[i][r] * ik;
+                sq[buffer][j][lane + 32 * r] = pq[i][r] * iq;
+            }
+            if (lane < COLUMNS) sv[buffer][j][lane] = pv[i];
+            if (lane == 0) {
+                float decay, step;
+                if (MODE == MODE_DELTA) {
+                    decay = expf(-a_rate * softplus_f(pdecay[i] + bias));
+                    step = 1.0f / (1.0f + expf(-pstep[i]));
+                } else {
+                    step = softplus_f(pdecay[i] + bias);
+                    decay = expf(-a_rate * step);
+                }
+                sdecay[buffer][j] = decay;
+                sstep[buffer][j] = step;
+            }
         }
-        float u;
-        if (MODE == MODE_DELTA) {
-            float dot = 0.f;
+    };
+
+    prefetch(t0);
+    publish(0);
+    __syncthreads();
+    int buffer = 0;
+    for (int first = t0; first < t1; first += CT, buffer ^= 1) {
+        const bool more = first + CT < t1;
+        if (more) prefetch(first + CT);  // in flight while this chunk is walked
+        const int count = min(CT, t1 - first);
+        for (int j = 0; j < count; ++j) {
+            const float decay = sdecay[buffer][j], step = sstep[buffer][j], cv = sv[buffer][j][cw];
+            float ck[NG][4], cq[NG][4];
+#pragma unroll
+            for (int r = 0; r < NG; ++r) {
+                const float4 k4 = *reinterpret_cast<const float4*>(&sk[buffer][j][4 * (LPC * r + l)]);
+                const float4 q4 = *reinterpret_cast<const float4*>(&sq[buffer][j][4 * (LPC * r + l)]);
+                ck[r][0] = k4.x; ck[r][1] = k4.y; ck[r][2] = k4.z; ck[r][3] = k4.w;
+                cq[r][0] = q4.x; cq[r][1] = q4.y; cq[r][2] = q4.z; cq[r][3] = q4.w;
+            }
+            float u;
+            if (MODE == MODE_DELTA) {
+                float part[4] = {0.f, 0.f, 0.f, 0.f};  // four chains instead of one: the sum's order is fixed all the same
+#pragma unroll
+                for (int r = 0; r < NG; ++r)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { s[r][i] *= decay; part[i] = fmaf(s[r][i], ck[r][i], part[i]); }
+                float dot = (part[0] + part[1]) + (part[2] + part[3]);
+#pragma unroll
+                for (int offset = 1; offset < LPC; offset <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, offset);
+                u = step * (cv - dot);
+            } else {
+#pragma unroll
+                for (int r = 0; r < NG; ++r)
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) s[r][i] *= decay;
+                u = step * cv;
+            }
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int r = 0; r < NG; ++r)
 #pragma unroll
-                for (int j = 0; j < 4; ++j) { s[r][j] *= decay; dot = fmaf(s[r][j], ck[r][j], dot); }
+                for (int i = 0; i < 4; ++i) { s[r][i] = fmaf(ck[r][i], u, s[r][i]); part[i] = fmaf(s[r][i], cq[r][i], part[i]); }
+            float o = (part[0] + part[1]) + (part[2] + part[3]);
 #pragma unroll
-            for (int offset = 1; offset < 8; offset <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, offset);
-            u = step * (cv - dot);
-        } else {
-#pragma unroll
-            for (int r = 0; r < NG; ++r)
-#pragma unroll
-                for (int j = 0; j < 4; ++j) s[r][j] *= decay;
-            u = step * cv;
+            for (int offset = 1; offset < LPC; offset <<= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
+            if (MODE == MODE_STATE_SPACE) o = fmaf(skip, cv, o);
+            if (l == 0 && col_ok) a.out[((size_t)(first + j) * a.heads + head) * a.e + col] = o;
         }
-        float o = 0.f;
-#pragma unroll
-        for (int r = 0; r < NG; ++r)
-#pragma unroll
-            for (int j = 0; j < 4; ++j) { s[r][j] = fmaf(ck[r][j], u, s[r][j]); o = fmaf(s[r][j], cq[r][j], o); }
-#pragma unroll
-        for (int offset = 1; offset < 8; offset <<= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
-        if (MODE == MODE_STATE_SPACE) o = fmaf(skip, cv, o);
-        if (l == 0 && col_ok) a.out[(size_t)t * a.heads * a.e + (size_t)head * a.e + col] = o;
+        if (!more) break;
+        publish(buffer ^ 1);
+        __syncthreads();
     }
 #pragma unroll
     for (int r = 0; r < NG; ++r) {
-        const int base = 32 * r + 4 * l;
+        const int base = 4 * (LPC * r + l);
         if (col_ok && base < a.n_padded) *reinterpret_cast<float4*>(mine + base) = make_float4(s[r][0], s[r][1], s[r][2], s[r][3]);
     }
 }
 
 template <int MODE>
 int launch_scan(const ScanArgs& a, int rows, cudaStream_t stream) {
-    const dim3 grid((a.e + SCAN_COLUMNS - 1) / SCAN_COLUMNS, a.heads, rows);
-    if (a.n <= 32) state_scan_kernel<1, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
-    else if (a.n <= 64) state_scan_kernel<2, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
-    else if (a.n <= 128) state_scan_kernel<4, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
-    else state_scan_kernel<8, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
+    // Eight lanes per column whatever the batch (a token's sums must not change with it).  Sixteen and thirty-two lanes were
+    // measured on a B200 at heads x e = 2,048 and 4,096 with n = 128: more warps, but every warp reads the whole key and query of
+    // every token whatever it owns of the state, and a prompt's scan took 1.3 to 2 times as long.
+    constexpr int LANES = 8;
+    const int per_lane = (a.n_padded + 4 * LANES - 1) / (4 * LANES);  // groups of four entries per lane
+    const dim3 grid((a.e + 128 / LANES - 1) / (128 / LANES), a.heads, rows);
+    if (per_lane <= 1) state_scan_kernel<1, LANES, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
+    else if (per_lane <= 2) state_scan_kernel<2, LANES, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
+    else if (per_lane <= 4) state_scan_kernel<4, LANES, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
+    else state_scan_kernel<8, LANES, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
     return launch_status();
 }
 
@@ -226,6 +266,34 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, int y_strid
         out[(size_t)t * out_stride + first + j] = from_float<TO>(v);
     }
 }
+
+// The same for groups of up to 1,024 columns: a warp per (token, group), four of them in a block; the lanes' partial sums
+// meet in a butterfly of fixed shape.
+template <typename TO>
+__global__ void gated_group_norm_warp_kernel(const float* __restrict__ y, int y_stride, const float* __restrict__ gate, int gate_stride,
+                                             int gate_off, const float* __restrict__ weight, int weight_len, int group, int groups, int gate_first,
+                                             float eps, TO* __restrict__ out, int out_stride) {
+    const int t = blockIdx.x, which = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (which >= groups) return;
+    const int first = which * group;
+    const float* yrow = y + (size_t)t * y_stride + first;
+    const float* grow = gate + (size_t)t * gate_stride + gate_off + first;
+    float sum = 0.f;
+    for (int j = lane; j < group; j += 32) {
+        float v = yrow[j];
+        if (gate_first) v *= silu_f(grow[j]);
+        sum = fmaf(v, v, sum);
+    }
+    const float inv = 1.0f / sqrtf(warp_sum(sum) / (float)group + eps);
+    for (int j = lane; j < group; j += 32) {
+        const float g = silu_f(grow[j]);
+        float v = yrow[j];
+        if (gate_first) v *= g;
+        v = v * inv * weight[(first + j) % weight_len];
+        if (!gate_first) v *= g;
+        out[(size_t)t * out_stride + first + j] = from_float<TO>(v);
+    }
+}
 }  // namespace
 
 HB_EXPORT int hb_causal_conv_silu(const float* x, int x_stride, int col0, int channels, const float* weight, const float* bias, int taps,
@@ -233,9 +301,11 @@ HB_EXPORT int hb_causal_conv_silu(const float* x, int x_stride, int col0, int ch
                                   const int* row_start, float* out, int tokens, cudaStream_t stream) {
     if (tokens <= 0 || channels <= 0) return 0;
     if (taps < 1) return HB_BAD_ARGUMENT;
-    const size_t total = (size_t)tokens * channels;
-    causal_conv_silu_kernel<<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(x, x_stride, col0, channels, weight, bias, taps, state,
-                                                                                (size_t)slot_stride, state_off, slots, token_row, row_start, out, total);
+    for (int first = 0; first < tokens; first += 65535) {  // the grid's second dimension holds 65,535 tokens
+        const int count = tokens - first < 65535 ? tokens - first : 65535;
+        causal_conv_silu_kernel<<<dim3((channels + 255) / 256, count), 256, 0, stream>>>(x, x_stride, col0, channels, weight, bias, taps, state, (size_t)slot_stride,
+                                                                                        state_off, slots, token_row, row_start, out, first);
+    }
     return launch_status();
 }
 
@@ -270,7 +340,17 @@ HB_EXPORT int hb_gated_group_norm(const float* y, int y_stride, const float* gat
                                   int tokens, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (group <= 0 || groups <= 0 || groups > 65535 || weight_len <= 0) return HB_UNSUPPORTED_SIZE;
-    const int threads = group >= 1024 ? 256 : (group >= 128 ? 128 : 64);
+    if (group <= 1024) {
+        const dim3 warps(tokens, (groups + 3) / 4);
+        if (out_is_bf16)
+            gated_group_norm_warp_kernel<<<warps, 128, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, groups, gate_first,
+                                                                    eps, (__nv_bfloat16*)out, out_stride);
+        else
+            gated_group_norm_warp_kernel<<<warps, 128, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, groups, gate_first,
+                                                                    eps, (float*)out, out_stride);
+        return launch_status();
+    }
+    const int threads = 256;
     const dim3 grid(tokens, groups);
     if (out_is_bf16)
         gated_group_norm_kernel<<<grid, threads, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, gate_first, eps,
