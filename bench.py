@@ -415,6 +415,8 @@ def nunivik_kernels(size: dict, measured: dict) -> dict:
         y = torch.randn(tokens, width, device=dev).to(torch.bfloat16)
         weight = torch.ones(width, device=dev)
         report(f"rmsnorm_add/{shape}", timed(lambda: ops.rmsnorm_add(h, y, weight, 1e-6, copy_dtype=torch.bfloat16)), tokens * width * (4 + 4 + 2 + 2))
+        # the like kernel of the closest model: its residual add fused with the norm that reads the sum
+        report(f"qwen2.add_rmsnorm/{shape}", timed(lambda: ops.add_rmsnorm(h, y, weight, 1e-6, torch.bfloat16)), tokens * width * (4 + 4 + 2 + 2))
         for kind, mode in (("delta", recurrent.MODE_DELTA), ("mamba2", recurrent.MODE_STATE_SPACE)):
             if kind == "delta":
                 heads, groups, n, e = size["delta"]

@@ -411,3 +411,24 @@ def test_replay_through_the_command(folders, dtype, tmp_path):
                 3: [ref["c"][49], ref["a"][69]]}
     for step, rows in expected.items():
         assert relative_error(read(step), np.stack(rows)) <= TOLERANCE[dtype], step
+
+
+def test_the_command_line_writes_a_random_model_and_generates_with_it(tmp_path):
+    """``python -m hyperion_b200 random`` from a config.json of this design, then ``generate`` on the folder it wrote:
+    the tokens are the plain implementation's greedy ones."""
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(CONFIGS["B"]))
+    folder = tmp_path / "model"
+    run = lambda *args: subprocess.run([sys.executable, "-m", "hyperion_b200", *args], capture_output=True, text=True, timeout=900, cwd=ROOT)
+    done = run("random", "--config", str(config), "--out", str(folder), "--seed", "5", "--std", "0.3")
+    assert done.returncode == 0, done.stderr[-2000:]
+    prompt = ids_for(71, 19, CONFIGS["B"]["vocab"])
+    done = run("generate", "-m", str(folder), "--dtype", "float32", "--prompt-ids", ",".join(map(str, prompt)), "--max-tokens", "5", "--temperature", "0",
+               "--ignore-eos", "--max-batch", "2")
+    assert done.returncode == 0, done.stderr[-2000:]
+    got = json.loads(done.stdout.strip().splitlines()[-1])
+    plain_config, weights = plain.read_model_folder(folder)
+    ids = list(prompt)
+    for _ in range(5):
+        ids.append(int(plain.forward(plain_config, weights, ids)[-1].argmax()))
+    assert got["tokens"] == ids[len(prompt):] and got["finish_reason"] == "length"
