@@ -79,39 +79,45 @@ struct ScanArgs {
     float q_scale;
 };
 
-template <int NG, int LPC, int MODE>  // NG groups of four entries per lane, LPC lanes per column: n <= NG * 4 * LPC
+template <int NG, int LPC, int CPT, int MODE>  // NG groups of four entries per lane, LPC lanes per column (n <= NG * 4 * LPC), CPT columns per thread
 __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs a) {
     // The tokens of the row pass through shared memory in chunks: while the block walks one chunk, every warp holds the next
     // chunk's share (every fourth token) in registers, already asked from memory; after the walk it turns them into what the
     // walk needs (unit keys and queries, decay, step) and writes them to the other buffer.  Nothing of that preparation lies on
-    // the chain from one token's state to the next.
-    constexpr int NP = NG * 4 * LPC, NPR = NP / 32, COLUMNS = 128 / LPC, CT = NP >= 256 ? 8 : 16, PER_WARP = CT / 4;
+    // the chain from one token's state to the next.  A thread owns its part of CPT columns: a token's key and query are read
+    // from shared memory once for all of them, and the columns' chains, which never meet, fill one another's waits (a prompt
+    // gives the GPU fewer warps than it has schedulers, so nothing else would).
+    constexpr int NP = NG * 4 * LPC, NPR = NP / 32, GROUPS = 128 / LPC, COLUMNS = GROUPS * CPT, VR = (COLUMNS + 31) / 32;
+    constexpr int CT = NP >= 256 ? 8 : 16, PER_WARP = CT / 4;
     __shared__ __align__(16) float sk[2][CT][NP];
     __shared__ __align__(16) float sq[2][CT][NP];
-    __shared__ float sv[2][CT][COLUMNS], sdecay[2][CT], sstep[2][CT];
+    __shared__ float sv[2][CT][VR * 32], sdecay[2][CT], sstep[2][CT];
 
     const int row = blockIdx.z, head = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int l = lane % LPC, cw = warp * (32 / LPC) + lane / LPC;
-    const int col0 = blockIdx.x * COLUMNS, col = col0 + cw;
-    const bool col_ok = col < a.e;
+    const int l = lane % LPC, cw = warp * (32 / LPC) + lane / LPC;  // this thread's columns: col0 + cw + GROUPS * c
+    const int col0 = blockIdx.x * COLUMNS;
     const int t0 = a.row_start[row], t1 = a.row_start[row + 1];
     const int group = head / (a.heads / a.groups);
-    float* mine = a.state + (size_t)a.slots[row] * a.slot_stride + a.state_off + ((size_t)head * a.e + (col_ok ? col : 0)) * a.n_padded;
+    float* const head_state = a.state + (size_t)a.slots[row] * a.slot_stride + a.state_off + (size_t)head * a.e * a.n_padded;
 
-    float s[NG][4];
+    float s[CPT][NG][4];
 #pragma unroll
-    for (int r = 0; r < NG; ++r) {
-        const int base = 4 * (LPC * r + l);
-        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (col_ok && base < a.n_padded) v = *reinterpret_cast<const float4*>(mine + base);
-        s[r][0] = v.x; s[r][1] = v.y; s[r][2] = v.z; s[r][3] = v.w;
+    for (int c = 0; c < CPT; ++c) {
+        const int col = col0 + cw + GROUPS * c;
+#pragma unroll
+        for (int r = 0; r < NG; ++r) {
+            const int base = 4 * (LPC * r + l);
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (col < a.e && base < a.n_padded) v = *reinterpret_cast<const float4*>(head_state + (size_t)col * a.n_padded + base);
+            s[c][r][0] = v.x; s[c][r][1] = v.y; s[c][r][2] = v.z; s[c][r][3] = v.w;
+        }
     }
     const float a_rate = expf(a.a_log[head]);
     const float bias = a.dt_bias[head];
     const float skip = MODE == MODE_STATE_SPACE ? a.skip[head] : 0.f;
 
-    float pk[PER_WARP][NPR], pq[PER_WARP][NPR], pv[PER_WARP], pdecay[PER_WARP], pstep[PER_WARP];
+    float pk[PER_WARP][NPR], pq[PER_WARP][NPR], pv[PER_WARP][VR], pdecay[PER_WARP], pstep[PER_WARP];
     auto prefetch = [&](int first) {
 #pragma unroll
         for (int i = 0; i < PER_WARP; ++i) {
@@ -126,7 +132,11 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
                 pk[i][r] = (live && index < a.n) ? k[index] : 0.f;
                 pq[i][r] = (live && index < a.n) ? q[index] : 0.f;
             }
-            pv[i] = (live && lane < COLUMNS && col0 + lane < a.e) ? c[a.v_off + (size_t)head * a.e + col0 + lane] : 0.f;
+#pragma unroll
+            for (int r = 0; r < VR; ++r) {
+                const int column = lane + 32 * r;
+                pv[i][r] = (live && column < COLUMNS && col0 + column < a.e) ? c[a.v_off + (size_t)head * a.e + col0 + column] : 0.f;
+            }
             const float* p = a.proj + (size_t)(live ? t : t0) * a.proj_stride;
             pdecay[i] = live ? p[a.decay_off + head] : 0.f;
             pstep[i] = (live && MODE == MODE_DELTA) ? p[a.step_off + head] : 0.f;
@@ -149,7 +159,8 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
                 sk[buffer][j][lane + 32 * r] = pk[i][r] * ik;
                 sq[buffer][j][lane + 32 * r] = pq[i][r] * iq;
             }
-            if (lane < COLUMNS) sv[buffer][j][lane] = pv[i];
+#pragma unroll
+            for (int r = 0; r < VR; ++r) sv[buffer][j][lane + 32 * r] = pv[i][r];
             if (lane == 0) {
                 float decay, step;
                 if (MODE == MODE_DELTA) {
@@ -174,7 +185,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
         if (more) prefetch(first + CT);  // in flight while this chunk is walked
         const int count = min(CT, t1 - first);
         for (int j = 0; j < count; ++j) {
-            const float decay = sdecay[buffer][j], step = sstep[buffer][j], cv = sv[buffer][j][cw];
+            const float decay = sdecay[buffer][j], step = sstep[buffer][j];
             float ck[NG][4], cq[NG][4];
 #pragma unroll
             for (int r = 0; r < NG; ++r) {
@@ -183,58 +194,89 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
                 ck[r][0] = k4.x; ck[r][1] = k4.y; ck[r][2] = k4.z; ck[r][3] = k4.w;
                 cq[r][0] = q4.x; cq[r][1] = q4.y; cq[r][2] = q4.z; cq[r][3] = q4.w;
             }
-            float u;
+            float cv[CPT], u[CPT], o[CPT];
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) cv[c] = sv[buffer][j][cw + GROUPS * c];
             if (MODE == MODE_DELTA) {
-                float part[4] = {0.f, 0.f, 0.f, 0.f};  // four chains instead of one: the sum's order is fixed all the same
+                float dot[CPT];
 #pragma unroll
-                for (int r = 0; r < NG; ++r)
+                for (int c = 0; c < CPT; ++c) {
+                    float part[4] = {0.f, 0.f, 0.f, 0.f};  // four chains instead of one: the sum's order is fixed all the same
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) { s[r][i] *= decay; part[i] = fmaf(s[r][i], ck[r][i], part[i]); }
-                float dot = (part[0] + part[1]) + (part[2] + part[3]);
+                    for (int r = 0; r < NG; ++r)
 #pragma unroll
-                for (int offset = 1; offset < LPC; offset <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, offset);
-                u = step * (cv - dot);
+                        for (int i = 0; i < 4; ++i) { s[c][r][i] *= decay; part[i] = fmaf(s[c][r][i], ck[r][i], part[i]); }
+                    dot[c] = (part[0] + part[1]) + (part[2] + part[3]);
+                }
+#pragma unroll
+                for (int offset = 1; offset < LPC; offset <<= 1)
+#pragma unroll
+                    for (int c = 0; c < CPT; ++c) dot[c] += __shfl_xor_sync(0xffffffffu, dot[c], offset);
+#pragma unroll
+                for (int c = 0; c < CPT; ++c) u[c] = step * (cv[c] - dot[c]);
             } else {
 #pragma unroll
+                for (int c = 0; c < CPT; ++c) {
+#pragma unroll
+                    for (int r = 0; r < NG; ++r)
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) s[c][r][i] *= decay;
+                    u[c] = step * cv[c];
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < CPT; ++c) {
+                float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
                 for (int r = 0; r < NG; ++r)
 #pragma unroll
-                    for (int i = 0; i < 4; ++i) s[r][i] *= decay;
-                u = step * cv;
+                    for (int i = 0; i < 4; ++i) { s[c][r][i] = fmaf(ck[r][i], u[c], s[c][r][i]); part[i] = fmaf(s[c][r][i], cq[r][i], part[i]); }
+                o[c] = (part[0] + part[1]) + (part[2] + part[3]);
             }
-            float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-            for (int r = 0; r < NG; ++r)
+            for (int offset = 1; offset < LPC; offset <<= 1)
 #pragma unroll
-                for (int i = 0; i < 4; ++i) { s[r][i] = fmaf(ck[r][i], u, s[r][i]); part[i] = fmaf(s[r][i], cq[r][i], part[i]); }
-            float o = (part[0] + part[1]) + (part[2] + part[3]);
+                for (int c = 0; c < CPT; ++c) o[c] += __shfl_xor_sync(0xffffffffu, o[c], offset);
 #pragma unroll
-            for (int offset = 1; offset < LPC; offset <<= 1) o += __shfl_xor_sync(0xffffffffu, o, offset);
-            if (MODE == MODE_STATE_SPACE) o = fmaf(skip, cv, o);
-            if (l == 0 && col_ok) a.out[((size_t)(first + j) * a.heads + head) * a.e + col] = o;
+            for (int c = 0; c < CPT; ++c) {
+                const int col = col0 + cw + GROUPS * c;
+                const float out = MODE == MODE_STATE_SPACE ? fmaf(skip, cv[c], o[c]) : o[c];
+                if (l == 0 && col < a.e) a.out[((size_t)(first + j) * a.heads + head) * a.e + col] = out;
+            }
         }
         if (!more) break;
         publish(buffer ^ 1);
         __syncthreads();
     }
 #pragma unroll
-    for (int r = 0; r < NG; ++r) {
-        const int base = 4 * (LPC * r + l);
-        if (col_ok && base < a.n_padded) *reinterpret_cast<float4*>(mine + base) = make_float4(s[r][0], s[r][1], s[r][2], s[r][3]);
+    for (int c = 0; c < CPT; ++c) {
+        const int col = col0 + cw + GROUPS * c;
+#pragma unroll
+        for (int r = 0; r < NG; ++r) {
+            const int base = 4 * (LPC * r + l);
+            if (col < a.e && base < a.n_padded)
+                *reinterpret_cast<float4*>(head_state + (size_t)col * a.n_padded + base) = make_float4(s[c][r][0], s[c][r][1], s[c][r][2], s[c][r][3]);
+        }
     }
 }
 
 template <int MODE>
 int launch_scan(const ScanArgs& a, int rows, cudaStream_t stream) {
-    // Eight lanes per column whatever the batch (a token's sums must not change with it).  Sixteen and thirty-two lanes were
-    // measured on a B200 at heads x e = 2,048 and 4,096 with n = 128: more warps, but every warp reads the whole key and query of
-    // every token whatever it owns of the state, and a prompt's scan took 1.3 to 2 times as long.
+    // Eight lanes per column; one column per thread for the delta rule, two for the state-space recurrence, whatever the batch (a
+    // token's sums must not change with it).  Measured on a B200 at heads x e = 2,048 and 4,096 with n = 128, a prompt of 2,048
+    // tokens: sixteen or thirty-two lanes per column (more warps, fewer entries each) took 1.3 to 2 times as long, because every
+    // warp reads the whole key and query of every token whatever it owns of the state.  More columns per thread go the other way:
+    // the state-space scan fell from 668 / 944 us to 498 / 660 us with two (986 with four), the delta rule, whose columns each add a
+    // reduction to the chain, rose from 783 / 939 us to 960 with two and 1,071 with four; eight decoded tokens gain a fifth either way.
     constexpr int LANES = 8;
     const int per_lane = (a.n_padded + 4 * LANES - 1) / (4 * LANES);  // groups of four entries per lane
-    const dim3 grid((a.e + 128 / LANES - 1) / (128 / LANES), a.heads, rows);
-    if (per_lane <= 1) state_scan_kernel<1, LANES, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
-    else if (per_lane <= 2) state_scan_kernel<2, LANES, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
-    else if (per_lane <= 4) state_scan_kernel<4, LANES, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
-    else state_scan_kernel<8, LANES, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
+    constexpr int PER_THREAD = MODE == MODE_STATE_SPACE ? 2 : 1;
+    const int columns = (128 / LANES) * PER_THREAD;
+    const dim3 grid((a.e + columns - 1) / columns, a.heads, rows);
+    if (per_lane <= 1) state_scan_kernel<1, LANES, PER_THREAD, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
+    else if (per_lane <= 2) state_scan_kernel<2, LANES, PER_THREAD, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
+    else if (per_lane <= 4) state_scan_kernel<4, LANES, PER_THREAD, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
+    else state_scan_kernel<8, LANES, PER_THREAD, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
     return launch_status();
 }
 
