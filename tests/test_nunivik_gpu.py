@@ -4,8 +4,8 @@ pages and state slots that are freed and taken again, keys at window and page bo
 sizes that differ in every respect between the configurations, and greedy generation through ``Engine.generate``.
 
 The configurations and weights are made here.  Weights are drawn so that a fault shows: query and key norm weights
-around 2 make the attention peaked, and where a test is about one key the input repeats a token so that this key's
-score stands out.  float32 runs are held to 3e-4 of the largest logit, which no wrong key, window edge or lost state
+around 2 make the attention peaked, and where a test is about one key a marker token, whose key points where the last
+query points, makes that key's score stand out.  float32 runs are held to 3e-4 of the largest logit, which no wrong key, window edge or lost state
 survives; bfloat16 runs to 5e-2 of a row's root-mean-square logit.
 """
 from __future__ import annotations
