@@ -8,7 +8,8 @@
 // (helios/crates/helios-hal/src/reference.rs:118-156; kernels/elementwise.cu:64-118).
 // Beyond the reference: keys and values may have different sizes per head and lie anywhere in a page
 // (the launcher gets their two base pointers and the strides of a page, a head and a token), and a
-// score may be capped smoothly, s <- cap * tanh(s / cap), before the softmax (cap 0 = no cap).
+// score may be capped smoothly, s <- cap * tanh(s / cap), before the softmax (cap 0 = no cap); a learned bias per head and
+// distance may be added to the score, and the result may pass a sigmoid gate.
 #include "common.cuh"
 
 namespace {
@@ -20,7 +21,8 @@ __global__ void __launch_bounds__(THREADS) attention_generic_kernel(
     const T* __restrict__ v_cache, size_t page_stride, size_t head_stride, int token_stride,
     const int* __restrict__ block_table, int table_width, const int* __restrict__ token_row,
     const int* __restrict__ positions, int heads, int kv_heads, int head_dim, int v_dim, int page_size, int pages, float scale,
-    float softcap, int window, int* status) {
+    float softcap, int window, const float* __restrict__ dist_bias, int bias_span, const float* __restrict__ gate, int gate_stride,
+    int gate_off, float out_scale, int* status) {
     __shared__ float qs[GMAX][DMAX];
     __shared__ float score[GMAX][TILE];
     __shared__ float m_run[GMAX], l_run[GMAX], alpha[GMAX];
@@ -86,6 +88,7 @@ __global__ void __launch_bounds__(THREADS) attention_generic_kernel(
                     if (lane == 0) {
                         float capped = s * scale;
                         if (softcap > 0.f) capped = softcap * tanhf(capped / softcap);
+                        if (dist_bias) capped += dist_bias[(size_t)(kvh * group + g0 + hh) * bias_span + min(pos - j, bias_span - 1)];
                         score[hh][jj] = page >= 0 ? capped : -INFINITY;
                     }
                 }
@@ -142,8 +145,10 @@ __global__ void __launch_bounds__(THREADS) attention_generic_kernel(
             for (int hh = 0; hh < GMAX; ++hh)
                 if (hh < g) {
                     const float l = l_run[hh];
-                    out[(size_t)t * out_stride + (size_t)(kvh * group + g0 + hh) * v_dim + d] =
-                        from_float<T>(l > 0.f ? acc[hh][c] / l : 0.f);
+                    const size_t column = (size_t)(kvh * group + g0 + hh) * v_dim + d;
+                    float result = l > 0.f ? acc[hh][c] / l : 0.f;
+                    if (gate) result *= out_scale / (1.f + expf(-gate[(size_t)t * gate_stride + gate_off + column]));
+                    out[(size_t)t * out_stride + column] = from_float<T>(result);
                 }
         }
     }
@@ -151,12 +156,16 @@ __global__ void __launch_bounds__(THREADS) attention_generic_kernel(
 }  // namespace
 
 // Keys at k_cache[page * page_stride + kv_head * head_stride + place * token_stride + i], i < head_dim; values likewise
-// from v_cache with i < v_dim (strides in elements).
-HB_EXPORT int hb_attention_general(const void* q, int q_stride, void* out, int out_stride, int is_bf16, const void* k_cache,
-                                   const void* v_cache, long long page_stride, long long head_stride, int token_stride,
-                                   const int* block_table, int table_width, const int* token_row, const int* positions,
-                                   int tokens, int heads, int kv_heads, int head_dim, int v_dim, int page_size, int pages, float scale,
-                                   float softcap, int window, int* status, cudaStream_t stream) {
+// from v_cache with i < v_dim (strides in elements).  dist_bias [heads, bias_span] float (optional): a score of query position p and
+// key position j takes dist_bias[head, min(p - j, bias_span - 1)] after scale and cap.  gate [tokens, gate_stride] float (optional): the
+// result of (token, head, d) is multiplied by out_scale * sigmoid(gate[token, gate_off + head * v_dim + d]) before its one rounding.
+HB_EXPORT int hb_attention_biased(const void* q, int q_stride, void* out, int out_stride, int is_bf16, const void* k_cache,
+                                  const void* v_cache, long long page_stride, long long head_stride, int token_stride,
+                                  const int* block_table, int table_width, const int* token_row, const int* positions,
+                                  int tokens, int heads, int kv_heads, int head_dim, int v_dim, int page_size, int pages, float scale,
+                                  float softcap, int window, const float* dist_bias, int bias_span, const float* gate, int gate_stride,
+                                  int gate_off, float out_scale, int* status, cudaStream_t stream) {
+    if (dist_bias && bias_span <= 0) return HB_BAD_ARGUMENT;
     if (tokens <= 0) return 0;
     if (head_dim <= 0 || head_dim > DMAX || v_dim <= 0 || v_dim > DMAX || kv_heads <= 0 || heads % kv_heads || page_size <= 0)
         return HB_UNSUPPORTED_SIZE;
@@ -167,13 +176,25 @@ HB_EXPORT int hb_attention_general(const void* q, int q_stride, void* out, int o
         attention_generic_kernel<<<grid, THREADS, 0, stream>>>((const __nv_bfloat16*)q, q_stride, (__nv_bfloat16*)out, out_stride,
                                                                (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, (size_t)page_stride,
                                                                (size_t)head_stride, token_stride, block_table, table_width, token_row,
-                                                               positions, heads, kv_heads, head_dim, v_dim, page_size, pages, scale, softcap, window, status);
+                                                               positions, heads, kv_heads, head_dim, v_dim, page_size, pages, scale, softcap, window,
+                                                               dist_bias, bias_span, gate, gate_stride, gate_off, out_scale, status);
     else
         attention_generic_kernel<<<grid, THREADS, 0, stream>>>((const float*)q, q_stride, (float*)out, out_stride, (const float*)k_cache,
                                                                (const float*)v_cache, (size_t)page_stride, (size_t)head_stride, token_stride,
                                                                block_table, table_width, token_row, positions, heads, kv_heads,
-                                                               head_dim, v_dim, page_size, pages, scale, softcap, window, status);
+                                                               head_dim, v_dim, page_size, pages, scale, softcap, window, dist_bias, bias_span,
+                                                               gate, gate_stride, gate_off, out_scale, status);
     return launch_status();
+}
+
+HB_EXPORT int hb_attention_general(const void* q, int q_stride, void* out, int out_stride, int is_bf16, const void* k_cache,
+                                   const void* v_cache, long long page_stride, long long head_stride, int token_stride,
+                                   const int* block_table, int table_width, const int* token_row, const int* positions,
+                                   int tokens, int heads, int kv_heads, int head_dim, int v_dim, int page_size, int pages, float scale,
+                                   float softcap, int window, int* status, cudaStream_t stream) {
+    return hb_attention_biased(q, q_stride, out, out_stride, is_bf16, k_cache, v_cache, page_stride, head_stride, token_stride, block_table,
+                               table_width, token_row, positions, tokens, heads, kv_heads, head_dim, v_dim, page_size, pages, scale, softcap,
+                               window, nullptr, 0, nullptr, 0, 0, 1.f, status, stream);
 }
 
 // Keys and values of one size in pages of [2, kv_heads, page_size, head_dim], no cap.

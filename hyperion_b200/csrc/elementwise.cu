@@ -666,3 +666,149 @@ HB_EXPORT int hb_stream_copy(const float* h, void* copy, long long count, cudaSt
     stream_copy_kernel<<<blocks, 256, 0, stream>>>(h, (__nv_bfloat16*)copy, (size_t)count);
     return launch_status();
 }
+
+// ---------------------------------------------------------------- norm of a sublayer's output + residual add + the next sublayer's norm
+// For blocks that normalise both what a sublayer reads and what it returns (x <- x + norm_b(f(norm_a(x)))), one launch per
+// sublayer boundary:   h[t] += y[t] / sqrt(mean(y[t]^2) + eps) * w_post (+ offset);   out[i] = h[t] / sqrt(mean(h[t]^2) + eps) * w_next.
+// Every piece is optional: without y only the offset is added, without w_next nothing is normalised for a reader.  With `rows`
+// only the listed rows are worked on and h is left as it was (the last norm of a model, where only some rows are read).
+// Everything is float; sums of squares are taken in a fixed order per row.
+template <typename TY, typename TO>
+__global__ void norm_add_norm_kernel(float* __restrict__ h, const TY* __restrict__ y, const float* __restrict__ w_post,
+                                     const float* __restrict__ offset, const float* __restrict__ w_next, TO* __restrict__ out,
+                                     const int* __restrict__ rows, int hidden, float eps_post, float eps_next) {
+    extern __shared__ float row_values[];
+    __shared__ float scratch[32];
+    const int i = blockIdx.x, t = rows ? rows[i] : i;
+    float* hrow = h + (size_t)t * hidden;
+    const TY* yrow = y ? y + (size_t)t * hidden : nullptr;
+    float inv_y = 0.f;
+    if (yrow) {
+        float sum = 0.f;
+        for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+            const float v = to_float(yrow[j]);
+            sum = fmaf(v, v, sum);
+        }
+        inv_y = 1.0f / sqrtf(block_sum(sum, scratch) / (float)hidden + eps_post);
+    }
+    float sum = 0.f;
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) {
+        float v = hrow[j];
+        if (yrow) v += to_float(yrow[j]) * inv_y * w_post[j];
+        if (offset) v += offset[j];
+        row_values[j] = v;
+        if (!rows) hrow[j] = v;
+        sum = fmaf(v, v, sum);
+    }
+    if (!w_next) return;
+    const float inv_h = 1.0f / sqrtf(block_sum(sum, scratch) / (float)hidden + eps_next);
+    for (int j = threadIdx.x; j < hidden; j += blockDim.x) out[(size_t)i * hidden + j] = from_float<TO>(row_values[j] * inv_h * w_next[j]);
+}
+
+// The same for bfloat16 sublayer outputs and readers in rows of up to 8,192 values, a multiple of 8: a thread keeps its 8 values
+// in registers through both norms (one trip to memory), with 16-byte accesses.
+__global__ void norm_add_norm_bf16x8_kernel(float* __restrict__ h, const __nv_bfloat16* __restrict__ y, const float* __restrict__ w_post,
+                                            const float* __restrict__ offset, const float* __restrict__ w_next, __nv_bfloat16* __restrict__ out,
+                                            const int* __restrict__ rows, int hidden, float eps_post, float eps_next) {
+    __shared__ float scratch[32];
+    const int i = blockIdx.x, t = rows ? rows[i] : i, j = threadIdx.x * 8;
+    const bool active = j < hidden;
+    float v[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float inv_y = 0.f;
+    if (y) {
+        if (active) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(y + (size_t)t * hidden + j);
+            const __nv_bfloat162* pairs = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                const float2 f = __bfloat1622float2(pairs[k]);
+                v[2 * k] = f.x; v[2 * k + 1] = f.y;
+            }
+        }
+        float sum = 0.f;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) sum = fmaf(v[k], v[k], sum);
+        inv_y = 1.0f / sqrtf(block_sum(sum, scratch) / (float)hidden + eps_post);
+    }
+    float x[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+    float* hrow = h + (size_t)t * hidden + j;
+    if (active) {
+        const float4 h0 = *reinterpret_cast<const float4*>(hrow), h1 = *reinterpret_cast<const float4*>(hrow + 4);
+        x[0] = h0.x; x[1] = h0.y; x[2] = h0.z; x[3] = h0.w; x[4] = h1.x; x[5] = h1.y; x[6] = h1.z; x[7] = h1.w;
+        if (y) {
+            const float4 w0 = *reinterpret_cast<const float4*>(w_post + j), w1 = *reinterpret_cast<const float4*>(w_post + j + 4);
+            const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+#pragma unroll
+            for (int k = 0; k < 8; ++k) x[k] += v[k] * inv_y * w[k];
+        }
+        if (offset) {
+            const float4 o0 = *reinterpret_cast<const float4*>(offset + j), o1 = *reinterpret_cast<const float4*>(offset + j + 4);
+            x[0] += o0.x; x[1] += o0.y; x[2] += o0.z; x[3] += o0.w; x[4] += o1.x; x[5] += o1.y; x[6] += o1.z; x[7] += o1.w;
+        }
+        if (!rows) {
+            *reinterpret_cast<float4*>(hrow) = make_float4(x[0], x[1], x[2], x[3]);
+            *reinterpret_cast<float4*>(hrow + 4) = make_float4(x[4], x[5], x[6], x[7]);
+        }
+    }
+    if (!w_next) return;
+    float sum = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; ++k) sum = fmaf(x[k], x[k], sum);
+    const float inv_h = 1.0f / sqrtf(block_sum(sum, scratch) / (float)hidden + eps_next);
+    if (!active) return;
+    const float4 n0 = *reinterpret_cast<const float4*>(w_next + j), n1 = *reinterpret_cast<const float4*>(w_next + j + 4);
+    uint4 packed;
+    __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&packed);
+    o[0] = __floats2bfloat162_rn(x[0] * inv_h * n0.x, x[1] * inv_h * n0.y);
+    o[1] = __floats2bfloat162_rn(x[2] * inv_h * n0.z, x[3] * inv_h * n0.w);
+    o[2] = __floats2bfloat162_rn(x[4] * inv_h * n1.x, x[5] * inv_h * n1.y);
+    o[3] = __floats2bfloat162_rn(x[6] * inv_h * n1.z, x[7] * inv_h * n1.w);
+    *reinterpret_cast<uint4*>(out + (size_t)i * hidden + j) = packed;
+}
+
+HB_EXPORT int hb_norm_add_norm(float* h, const void* y, int y_is_bf16, const float* w_post, const float* offset, const float* w_next, void* out,
+                               int out_is_bf16, const int* rows, int n_rows, int hidden, float eps_post, float eps_next, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (hidden <= 0 || hidden > 49152 || (y && !w_post) || (w_next && !out)) return HB_BAD_ARGUMENT;
+    const bool halves = (!y || y_is_bf16) && (!w_next || out_is_bf16);
+    if (halves && hidden % 8 == 0 && hidden <= 8192 &&
+        (((uintptr_t)h | (uintptr_t)y | (uintptr_t)w_post | (uintptr_t)offset | (uintptr_t)w_next | (uintptr_t)out) & 15) == 0) {
+        const int lanes = ((hidden / 8 + 31) / 32) * 32;  // which kernel runs follows from the width and the types alone
+        norm_add_norm_bf16x8_kernel<<<n_rows, lanes, 0, stream>>>(h, (const __nv_bfloat16*)y, w_post, offset, w_next, (__nv_bfloat16*)out, rows, hidden,
+                                                                  eps_post, eps_next);
+        return launch_status();
+    }
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    const size_t shared = (size_t)hidden * sizeof(float);
+#define HB_NORM_ADD_NORM(TY, TO)                                                                                                          \
+    do {                                                                                                                                  \
+        if (shared > 48 * 1024) cudaFuncSetAttribute(norm_add_norm_kernel<TY, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared); \
+        norm_add_norm_kernel<TY, TO><<<n_rows, threads, shared, stream>>>(h, (const TY*)y, w_post, offset, w_next, (TO*)out, rows, hidden,   \
+                                                                         eps_post, eps_next);                                            \
+    } while (0)
+    const bool y16 = y && y_is_bf16, o16 = w_next && out_is_bf16;
+    if (y16 && o16) HB_NORM_ADD_NORM(__nv_bfloat16, __nv_bfloat16);
+    else if (y16) HB_NORM_ADD_NORM(__nv_bfloat16, float);
+    else if (o16) HB_NORM_ADD_NORM(float, __nv_bfloat16);
+    else HB_NORM_ADD_NORM(float, float);
+#undef HB_NORM_ADD_NORM
+    return launch_status();
+}
+
+// ---------------------------------------------------------------- GELU in its tanh form
+// out = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), in float, rounded once.
+template <typename T>
+__global__ void gelu_tanh_kernel(const T* __restrict__ x, T* __restrict__ out, size_t count) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < count; i += (size_t)gridDim.x * blockDim.x) {
+        const float z = to_float(x[i]);
+        out[i] = from_float<T>(0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))));
+    }
+}
+
+HB_EXPORT int hb_gelu_tanh(const void* x, void* out, int is_bf16, long long count, cudaStream_t stream) {
+    if (count <= 0) return 0;
+    const int blocks = (int)((count + 255) / 256 < 8192 ? (count + 255) / 256 : 8192);
+    if (is_bf16) gelu_tanh_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, (size_t)count);
+    else gelu_tanh_kernel<<<blocks, 256, 0, stream>>>((const float*)x, (float*)out, (size_t)count);
+    return launch_status();
+}

@@ -104,3 +104,103 @@ HB_EXPORT int hb_heads_prepare(void* x, int is_bf16, int tokens, int stride, int
                                                            table_width, token_row, page_size, pages, status);
     return launch_status();
 }
+
+// ---------------------------------------------------------------- the same from float projections, with more choices
+// The projections arrive as float rows (a product kept in float so that norms, rotations and recurrences never see a
+// 16-bit value); queries go to a dense buffer of the attention's element type (or stay float, in place, for a recurrence),
+// keys and values to their cache pages or to dense buffers.  Further choices:
+//   * the RMS norm of queries (and of keys) may run over the whole projection, all heads at once, with a weight per
+//     column of the projection (norm_whole), instead of per head with one weight for all heads,
+//   * the rotation may pair dimension i with i + rot_dims / 2 (rot_half) instead of 2i with 2i + 1,
+//   * keys are multiplied by k_scale after the rotation.
+// Every thread reads and writes whole pairs, so the float-to-float case may work in place.
+namespace {
+template <typename TO>
+__global__ void __launch_bounds__(THREADS) heads_prepare_wide_kernel(
+    const float* x, int stride, int q_off, int k_off, int v_off, int q_heads, int kv_heads, int head_dim, int v_dim,
+    const float* __restrict__ q_norm, const float* __restrict__ k_norm, int norm_whole, float eps, const float* __restrict__ inv_freq,
+    int rot_dims, int rot_half, const int* __restrict__ positions, float k_scale, TO* q_out, int q_out_stride, TO* k_out, int k_out_stride,
+    TO* __restrict__ k_cache, TO* __restrict__ v_cache, size_t page_stride, size_t head_stride, int token_stride,
+    const int* __restrict__ block_table, int table_width, const int* __restrict__ token_row, int page_size, int pages, int* status) {
+    __shared__ float scratch[32];
+    const int t = blockIdx.x, head = blockIdx.y;  // q heads, then k heads, then v heads
+    const int pos = positions[t];
+    const float* row = x + (size_t)t * stride;
+    int page = -1, slot = 0;
+    if (k_cache && head >= q_heads) {
+        const int block = pos / page_size;
+        page = (pos >= 0 && block < table_width) ? block_table[(size_t)token_row[t] * table_width + block] : -1;
+        if (page < 0 || page >= pages) {
+            if (threadIdx.x == 0) atomicOr(status, HB_STATUS_BAD_PAGE);
+            page = -1;
+        }
+        slot = pos - block * page_size;
+    }
+    if (head < q_heads + kv_heads) {
+        const bool is_q = head < q_heads;
+        const int local = is_q ? head : head - q_heads, count = is_q ? q_heads : kv_heads;
+        const float* all = row + (is_q ? q_off : k_off);
+        const float* p = all + (size_t)local * head_dim;
+        const float* w = is_q ? q_norm : k_norm;
+        float inv = 1.f;
+        if (w) {
+            const float* from = norm_whole ? all : p;
+            const int width = norm_whole ? count * head_dim : head_dim;
+            float sum = 0.f;
+            for (int i = threadIdx.x; i < width; i += THREADS) sum = fmaf(from[i], from[i], sum);
+            inv = 1.0f / sqrtf(block_sum(sum, scratch) / (float)width + eps);
+            if (norm_whole) w += (size_t)local * head_dim;
+        }
+        TO* dst;
+        if (is_q) dst = q_out + (size_t)t * q_out_stride + (size_t)local * head_dim;
+        else if (k_cache) dst = page >= 0 ? k_cache + (size_t)page * page_stride + (size_t)local * head_stride + (size_t)slot * token_stride : nullptr;
+        else dst = k_out + (size_t)t * k_out_stride + (size_t)local * head_dim;
+        if (!dst) return;
+        const float post = is_q ? 1.f : k_scale;
+        const int pairs = inv_freq ? rot_dims / 2 : 0;
+        for (int i = threadIdx.x; i < pairs; i += THREADS) {
+            const int a = rot_half ? i : 2 * i, b = rot_half ? i + pairs : 2 * i + 1;
+            const float u = p[a] * inv * (w ? w[a] : 1.f), v = p[b] * inv * (w ? w[b] : 1.f);
+            float s, c;
+            sincosf((float)pos * inv_freq[i], &s, &c);
+            dst[a] = from_float<TO>((u * c - v * s) * post);
+            dst[b] = from_float<TO>((v * c + u * s) * post);
+        }
+        for (int i = 2 * pairs + threadIdx.x; i < head_dim; i += THREADS) dst[i] = from_float<TO>(p[i] * inv * (w ? w[i] : 1.f) * post);
+    } else {
+        const int vh = head - q_heads - kv_heads;
+        const float* p = row + v_off + (size_t)vh * v_dim;
+        TO* dst = page >= 0 ? v_cache + (size_t)page * page_stride + (size_t)vh * head_stride + (size_t)slot * token_stride : nullptr;
+        if (!dst) return;
+        for (int i = threadIdx.x; i < v_dim; i += THREADS) dst[i] = from_float<TO>(p[i]);
+    }
+}
+}  // namespace
+
+// x [tokens, stride] float with queries at q_off, keys at k_off, values at v_off.  q_out is always given; keys go to the cache
+// (k_cache and v_cache given, values too) or to k_out (values then stay where they are).
+HB_EXPORT int hb_heads_prepare_wide(const float* x, int tokens, int stride, int q_off, int k_off, int v_off, int q_heads, int kv_heads, int head_dim,
+                                    int v_dim, const float* q_norm, const float* k_norm, int norm_whole, float eps, const float* inv_freq, int rot_dims,
+                                    int rot_half, const int* positions, float k_scale, void* q_out, int q_out_stride, void* k_out, int k_out_stride,
+                                    int out_is_bf16, void* k_cache, void* v_cache, long long page_stride, long long head_stride, int token_stride,
+                                    const int* block_table, int table_width, const int* token_row, int page_size, int pages, int* status,
+                                    cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (head_dim <= 0 || v_dim <= 0 || rot_dims < 0 || rot_dims > head_dim || (rot_dims & 1) || !q_out || (!k_cache && !k_out)) return HB_UNSUPPORTED_SIZE;
+    const int heads = q_heads + kv_heads + (k_cache ? kv_heads : 0);
+    if (heads <= 0 || heads > 65535) return HB_UNSUPPORTED_SIZE;
+    const dim3 grid(tokens, heads);
+    if (out_is_bf16)
+        heads_prepare_wide_kernel<<<grid, THREADS, 0, stream>>>(x, stride, q_off, k_off, v_off, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, norm_whole,
+                                                                eps, inv_freq, rot_dims, rot_half, positions, k_scale, (__nv_bfloat16*)q_out, q_out_stride,
+                                                                (__nv_bfloat16*)k_out, k_out_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+                                                                (size_t)page_stride, (size_t)head_stride, token_stride, block_table, table_width, token_row,
+                                                                page_size, pages, status);
+    else
+        heads_prepare_wide_kernel<<<grid, THREADS, 0, stream>>>(x, stride, q_off, k_off, v_off, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, norm_whole,
+                                                                eps, inv_freq, rot_dims, rot_half, positions, k_scale, (float*)q_out, q_out_stride,
+                                                                (float*)k_out, k_out_stride, (float*)k_cache, (float*)v_cache, (size_t)page_stride,
+                                                                (size_t)head_stride, token_stride, block_table, table_width, token_row, page_size, pages,
+                                                                status);
+    return launch_status();
+}

@@ -1,0 +1,220 @@
+// Kernels of a feed-forward made of many small experts of which every token uses a few: the router, the plan that sorts
+// (token, choice) pairs by expert, the gather of the sorted rows, a grouped matrix product (every tile of rows multiplies its own
+// expert's matrix) and the sum of a token's experts.  Nothing here asks the host anything: the number of rows an expert gets
+// is known on the device only, so all buffers are sized by their worst case (every expert's rows padded to whole tiles) and
+// tiles beyond the last used one find -1 in the tile list and return.
+//
+//   route:    z = W_r x in float (one sequential chain of fixed shape per logit), the `top` largest logits by selection
+//             (lowest index first among equals), weight = sigmoid(z) of the chosen (not renormalised) or 1
+//   plan:     per expert a run of slots, padded to a multiple of `pad`; slot_of[token, choice]; per slot its token (or -1)
+//             and its weight; per tile of `pad` slots its expert (or -1)
+//   gather:   xs[slot] = weight * x[token] (the weight multiplies what the expert reads); padding rows are left as they are
+//   product:  C[slot] = A[slot] W[expert of slot's tile]^T, float accumulation in one chain over k per output
+//   combine:  out[token] = base[token] + sum over choices of y[slot_of[token, choice]], in the order of the choices
+#include "common.cuh"
+
+namespace {
+constexpr int ROUTE_THREADS = 128;
+
+template <typename T>
+__global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ router, int hidden,
+                                                                  int experts, int top, int weighted, int* __restrict__ chosen,
+                                                                  float* __restrict__ weights) {
+    extern __shared__ float shared[];  // the token's row, then one logit per expert
+    float* row = shared;
+    float* logit = shared + hidden;
+    const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < hidden; i += ROUTE_THREADS) row[i] = to_float(x[(size_t)t * x_stride + i]);
+    __syncthreads();
+    for (int e = warp; e < experts; e += ROUTE_THREADS / 32) {
+        const float* w = router + (size_t)e * hidden;
+        float sum = 0.f;
+        for (int i = lane; i < hidden; i += 32) sum = fmaf(row[i], w[i], sum);
+        sum = warp_sum(sum);
+        if (lane == 0) logit[e] = sum;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int k = 0; k < top; ++k) {
+            int best = -1;
+            float value = -INFINITY;
+            for (int e = 0; e < experts; ++e)
+                if (logit[e] > value || (best < 0 && logit[e] == value)) { best = e; value = logit[e]; }
+            if (best < 0) best = 0;  // only when every logit left is not a number
+            chosen[(size_t)t * top + k] = best;
+            weights[(size_t)t * top + k] = weighted ? 1.0f / (1.0f + expf(-value)) : 1.f;
+            logit[best] = -INFINITY;
+        }
+    }
+}
+
+constexpr int PLAN_THREADS = 1024;
+
+// One block.  counts and cursors live in shared memory (experts <= 1024).
+__global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const int* __restrict__ chosen, const float* __restrict__ weights, int pairs, int top,
+                                                                int experts, int pad, int capacity, int* __restrict__ slot_of,
+                                                                int* __restrict__ slot_token, float* __restrict__ slot_weight,
+                                                                int* __restrict__ tile_expert) {
+    __shared__ int count[1024], start[1024];
+    const int tid = threadIdx.x;
+    for (int e = tid; e < experts; e += PLAN_THREADS) count[e] = 0;
+    for (int s = tid; s < capacity; s += PLAN_THREADS) { slot_token[s] = -1; slot_weight[s] = 0.f; }
+    for (int i = tid; i < capacity / pad; i += PLAN_THREADS) tile_expert[i] = -1;
+    __syncthreads();
+    for (int i = tid; i < pairs; i += PLAN_THREADS) atomicAdd(&count[chosen[i]], 1);
+    __syncthreads();
+    if (tid == 0) {
+        int at = 0;
+        for (int e = 0; e < experts; ++e) {
+            start[e] = at;
+            const int tiles = (count[e] + pad - 1) / pad;
+            for (int i = 0; i < tiles; ++i) tile_expert[at / pad + i] = e;
+            at += tiles * pad;
+            count[e] = 0;  // from here on: the cursor inside the expert's run
+        }
+    }
+    __syncthreads();
+    // which slot of its expert's run a pair takes depends on the order of the atomics; a row's result does not depend on its slot
+    for (int i = tid; i < pairs; i += PLAN_THREADS) {
+        const int e = chosen[i];
+        const int slot = start[e] + atomicAdd(&count[e], 1);
+        slot_of[i] = slot;
+        slot_token[slot] = i / top;
+        slot_weight[slot] = weights[i];
+    }
+}
+
+template <typename T>
+__global__ void moe_gather_kernel(const T* __restrict__ x, int x_stride, const int* __restrict__ slot_token, const float* __restrict__ slot_weight,
+                                  T* __restrict__ out, int hidden) {
+    const int slot = blockIdx.x, t = slot_token[slot];
+    if (t < 0) return;  // padding: whatever the product makes of such a row, no one reads it, and rows do not meet in a product
+    const float w = slot_weight[slot];
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) out[(size_t)slot * hidden + i] = from_float<T>(to_float(x[(size_t)t * x_stride + i]) * w);
+}
+
+// C[slot, :] = A[slot, :] W[e]^T for the tile's expert e; W is [experts, n, k] dense.  Tiles of 64 x 64 outputs, 4 x 4 per thread, every
+// output one sequential chain of fused multiply-adds over k = 0..K-1 in float, whatever the element type.
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ a, const T* __restrict__ w, T* __restrict__ c, const int* __restrict__ tile_expert,
+                                                       int pad, int n, int k) {
+    __shared__ float as[BK][BM + 4];
+    __shared__ float ws[BK][BN + 4];
+    const int tid = threadIdx.x;
+    const int row0 = blockIdx.y * BM, col0 = blockIdx.x * BN;
+    const int expert = tile_expert[row0 / pad];
+    if (expert < 0) return;
+    const T* we = w + (size_t)expert * n * k;
+    const int ty = tid / 16, tx = tid % 16;
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+    const int lrow = tid / 4, lk = (tid % 4) * 4;
+    for (int k0 = 0; k0 < k; k0 += BK) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int kk = k0 + lk + e;
+            const int wr = col0 + lrow;
+            as[lk + e][lrow] = kk < k ? to_float(a[(size_t)(row0 + lrow) * k + kk]) : 0.f;
+            ws[lk + e][lrow] = (wr < n && kk < k) ? to_float(we[(size_t)wr * k + kk]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int kk = 0; kk < BK; ++kk) {
+            float av[TM], wv[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) av[i] = as[kk][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) wv[j] = ws[kk][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(av[i], wv[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int r = row0 + ty * TM + i;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int col = col0 + tx * TN + j;
+            if (col < n) c[(size_t)r * n + col] = from_float<T>(acc[i][j]);
+        }
+    }
+}
+
+template <typename TY, typename TB, typename TO>
+__global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ slot_of, int top, const TB* __restrict__ base, TO* __restrict__ out,
+                                   int hidden) {
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float sum = base ? to_float(base[(size_t)t * hidden + i]) : 0.f;
+        for (int k = 0; k < top; ++k) sum += to_float(y[(size_t)slot_of[(size_t)t * top + k] * hidden + i]);
+        out[(size_t)t * hidden + i] = from_float<TO>(sum);
+    }
+}
+}  // namespace
+
+HB_EXPORT int hb_moe_route(const void* x, int is_bf16, int x_stride, const float* router, int tokens, int hidden, int experts, int top, int weighted,
+                           int* chosen, float* weights, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    if (experts <= 0 || experts > 1024 || top <= 0 || top > experts || hidden <= 0) return HB_UNSUPPORTED_SIZE;
+    const size_t shared = (size_t)(hidden + experts) * sizeof(float);
+    if (shared > 200 * 1024) return HB_UNSUPPORTED_SIZE;
+    if (is_bf16) {
+        if (shared > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        moe_route_kernel<<<tokens, ROUTE_THREADS, shared, stream>>>((const __nv_bfloat16*)x, x_stride, router, hidden, experts, top, weighted, chosen, weights);
+    } else {
+        if (shared > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
+        moe_route_kernel<<<tokens, ROUTE_THREADS, shared, stream>>>((const float*)x, x_stride, router, hidden, experts, top, weighted, chosen, weights);
+    }
+    return launch_status();
+}
+
+// capacity: a multiple of pad, at least pairs + experts * (pad - 1) rounded up to it.  tile_expert has capacity / pad entries.
+HB_EXPORT int hb_moe_plan(const int* chosen, const float* weights, int pairs, int top, int experts, int pad, int capacity, int* slot_of,
+                          int* slot_token, float* slot_weight, int* tile_expert, cudaStream_t stream) {
+    if (pairs <= 0) return 0;
+    if (experts <= 0 || experts > 1024 || pad <= 0 || capacity % pad || top <= 0) return HB_UNSUPPORTED_SIZE;
+    if ((long long)capacity < (long long)pairs + (long long)experts * (pad - 1)) return HB_BAD_ARGUMENT;
+    moe_plan_kernel<<<1, PLAN_THREADS, 0, stream>>>(chosen, weights, pairs, top, experts, pad, capacity, slot_of, slot_token, slot_weight, tile_expert);
+    return launch_status();
+}
+
+HB_EXPORT int hb_moe_gather(const void* x, int is_bf16, int x_stride, const int* slot_token, const float* slot_weight, void* out, int capacity,
+                            int hidden, cudaStream_t stream) {
+    if (capacity <= 0) return 0;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (is_bf16) moe_gather_kernel<<<capacity, threads, 0, stream>>>((const __nv_bfloat16*)x, x_stride, slot_token, slot_weight, (__nv_bfloat16*)out, hidden);
+    else moe_gather_kernel<<<capacity, threads, 0, stream>>>((const float*)x, x_stride, slot_token, slot_weight, (float*)out, hidden);
+    return launch_status();
+}
+
+// a [capacity, k] and c [capacity, n] dense, w [experts, n, k] dense; pad a multiple of 64.
+HB_EXPORT int hb_moe_gemm(const void* a, const void* w, void* c, int is_bf16, const int* tile_expert, int pad, int capacity, int n, int k,
+                          cudaStream_t stream) {
+    if (capacity <= 0 || n <= 0) return 0;
+    if (k <= 0 || pad % BM || capacity % pad) return HB_BAD_ARGUMENT;
+    const dim3 grid((n + BN - 1) / BN, capacity / BM);
+    if (grid.y > 65535) return HB_UNSUPPORTED_SIZE;
+    if (is_bf16) moe_gemm_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)a, (const __nv_bfloat16*)w, (__nv_bfloat16*)c, tile_expert, pad, n, k);
+    else moe_gemm_kernel<<<grid, 256, 0, stream>>>((const float*)a, (const float*)w, (float*)c, tile_expert, pad, n, k);
+    return launch_status();
+}
+
+// y [capacity, hidden] and base [tokens, hidden] (optional) in the activation type; out in the same type.
+HB_EXPORT int hb_moe_combine(const void* y, const int* slot_of, int top, const void* base, void* out, int is_bf16, int tokens, int hidden,
+                             cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (is_bf16)
+        moe_combine_kernel<<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)y, slot_of, top, (const __nv_bfloat16*)base, (__nv_bfloat16*)out, hidden);
+    else
+        moe_combine_kernel<<<tokens, threads, 0, stream>>>((const float*)y, slot_of, top, (const float*)base, (float*)out, hidden);
+    return launch_status();
+}

@@ -9,6 +9,7 @@
 // token, with a key k, a query q (both of size n), a value v (size e), a decay a and a step b:
 //     delta rule:   S <- a S;  u = b (v - S^T k);  S <- S + k u^T;  o = S^T q
 //     state space:  S <- a S + k (b v)^T;                           o = S^T q + D v
+//     retention:    S <- a S + k v^T  (a fixed per head);           o = S^T q
 // Column j of S (one value dimension) never meets another column, so the work is cut by columns:
 // eight lanes share a column, each holding n / 8 of its entries in registers (groups of four
 // consecutive entries, stored as S^T so that they are one 16-byte access), and a block of 128
@@ -20,7 +21,7 @@
 
 namespace {
 constexpr int SCAN_THREADS = 128;
-enum : int { MODE_DELTA = 0, MODE_STATE_SPACE = 1 };
+enum : int { MODE_DELTA = 0, MODE_STATE_SPACE = 1, MODE_RETENTION = 2 };
 
 __device__ __forceinline__ float silu_f(float z) { return z / (1.f + expf(-z)); }
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.f ? z : log1pf(expf(z)); }
@@ -113,8 +114,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
             s[c][r][0] = v.x; s[c][r][1] = v.y; s[c][r][2] = v.z; s[c][r][3] = v.w;
         }
     }
-    const float a_rate = expf(a.a_log[head]);
-    const float bias = a.dt_bias[head];
+    const float a_rate = MODE == MODE_RETENTION ? 0.f : expf(a.a_log[head]);
+    const float fixed_decay = MODE == MODE_RETENTION ? a.a_log[head] : 0.f;
+    const float bias = MODE == MODE_RETENTION ? 0.f : a.dt_bias[head];
     const float skip = MODE == MODE_STATE_SPACE ? a.skip[head] : 0.f;
 
     float pk[PER_WARP][NPR], pq[PER_WARP][NPR], pv[PER_WARP][VR], pdecay[PER_WARP], pstep[PER_WARP];
@@ -138,7 +140,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
                 pv[i][r] = (live && column < COLUMNS && col0 + column < a.e) ? c[a.v_off + (size_t)head * a.e + col0 + column] : 0.f;
             }
             const float* p = a.proj + (size_t)(live ? t : t0) * a.proj_stride;
-            pdecay[i] = live ? p[a.decay_off + head] : 0.f;
+            pdecay[i] = (live && MODE != MODE_RETENTION) ? p[a.decay_off + head] : 0.f;
             pstep[i] = (live && MODE == MODE_DELTA) ? p[a.step_off + head] : 0.f;
         }
     };
@@ -166,6 +168,9 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
                 if (MODE == MODE_DELTA) {
                     decay = expf(-a_rate * softplus_f(pdecay[i] + bias));
                     step = 1.0f / (1.0f + expf(-pstep[i]));
+                } else if (MODE == MODE_RETENTION) {  // the head's decay is a constant of the model; keys enter as they are
+                    decay = fixed_decay;
+                    step = 1.f;
                 } else {
                     step = softplus_f(pdecay[i] + bias);
                     decay = expf(-a_rate * step);
@@ -270,7 +275,7 @@ int launch_scan(const ScanArgs& a, int rows, cudaStream_t stream) {
     // reduction to the chain, rose from 783 / 939 us to 960 with two and 1,071 with four; eight decoded tokens gain a fifth either way.
     constexpr int LANES = 8;
     const int per_lane = (a.n_padded + 4 * LANES - 1) / (4 * LANES);  // groups of four entries per lane
-    constexpr int PER_THREAD = MODE == MODE_STATE_SPACE ? 2 : 1;
+    constexpr int PER_THREAD = MODE == MODE_DELTA ? 1 : 2;
     const int columns = (128 / LANES) * PER_THREAD;
     const dim3 grid((a.e + columns - 1) / columns, a.heads, rows);
     if (per_lane <= 1) state_scan_kernel<1, LANES, PER_THREAD, MODE><<<grid, SCAN_THREADS, 0, stream>>>(a);
@@ -283,11 +288,11 @@ int launch_scan(const ScanArgs& a, int rows, cudaStream_t stream) {
 // ---------------------------------------------------------------- gated group norm
 // One block per (token, group of `group` columns).  gate_first: v = y * silu(g), out = v / rms(v) * w; otherwise
 // out = y / rms(y) * w * silu(g).  The weight has `weight_len` entries and is indexed by column % weight_len (a weight
-// of one head's size is shared by all heads).
+// of one head's size is shared by all heads; no weight at all: a plain unit RMS).  `scale` multiplies the result before its one rounding.
 template <typename TO>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, int y_stride, const float* __restrict__ gate, int gate_stride,
                                         int gate_off, const float* __restrict__ weight, int weight_len, int group, int gate_first,
-                                        float eps, TO* __restrict__ out, int out_stride) {
+                                        float eps, float scale, TO* __restrict__ out, int out_stride) {
     __shared__ float scratch[32];
     const int t = blockIdx.x, first = blockIdx.y * group;
     const float* yrow = y + (size_t)t * y_stride + first;
@@ -303,9 +308,9 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, int y_strid
         const float g = silu_f(grow[j]);
         float v = yrow[j];
         if (gate_first) v *= g;
-        v = v * inv * weight[(first + j) % weight_len];
+        v = v * inv * (weight ? weight[(first + j) % weight_len] : 1.f);
         if (!gate_first) v *= g;
-        out[(size_t)t * out_stride + first + j] = from_float<TO>(v);
+        out[(size_t)t * out_stride + first + j] = from_float<TO>(v * scale);
     }
 }
 
@@ -314,7 +319,7 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, int y_strid
 template <typename TO>
 __global__ void gated_group_norm_warp_kernel(const float* __restrict__ y, int y_stride, const float* __restrict__ gate, int gate_stride,
                                              int gate_off, const float* __restrict__ weight, int weight_len, int group, int groups, int gate_first,
-                                             float eps, TO* __restrict__ out, int out_stride) {
+                                             float eps, float scale, TO* __restrict__ out, int out_stride) {
     const int t = blockIdx.x, which = blockIdx.y * 4 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
     if (which >= groups) return;
     const int first = which * group;
@@ -331,9 +336,9 @@ __global__ void gated_group_norm_warp_kernel(const float* __restrict__ y, int y_
         const float g = silu_f(grow[j]);
         float v = yrow[j];
         if (gate_first) v *= g;
-        v = v * inv * weight[(first + j) % weight_len];
+        v = v * inv * (weight ? weight[(first + j) % weight_len] : 1.f);
         if (!gate_first) v *= g;
-        out[(size_t)t * out_stride + first + j] = from_float<TO>(v);
+        out[(size_t)t * out_stride + first + j] = from_float<TO>(v * scale);
     }
 }
 }  // namespace
@@ -360,6 +365,7 @@ HB_EXPORT int hb_conv_state_update(const float* x, int x_stride, int col0, int c
     return launch_status();
 }
 
+// mode 2: retention (decay = a_log[head] itself, a constant of the model; step = 1; keys, queries and values as given; proj, dt_bias and skip unused).
 // mode 0: gated delta rule (keys and queries made unit vectors, q times q_scale; decay = exp(-exp(a_log) softplus(proj[decay_off] + dt_bias)),
 // step = sigmoid(proj[step_off])).  mode 1: state space (step = softplus(proj[decay_off] + dt_bias), decay = exp(-exp(a_log) step), skip = D).
 // The state of (slot, head) is S^T [e, n_padded] at state + slot * slot_stride + state_off; n_padded, state_off and slot_stride are multiples of 4.
@@ -374,31 +380,194 @@ HB_EXPORT int hb_state_scan(int mode, const float* conv, int conv_stride, int k_
                state_off, slots, row_start, out, heads, groups, n, n_padded, e, q_scale};
     if (mode == MODE_DELTA) return launch_scan<MODE_DELTA>(a, rows, stream);
     if (mode == MODE_STATE_SPACE) return launch_scan<MODE_STATE_SPACE>(a, rows, stream);
+    if (mode == MODE_RETENTION) return launch_scan<MODE_RETENTION>(a, rows, stream);
     return HB_BAD_ARGUMENT;
 }
 
 HB_EXPORT int hb_gated_group_norm(const float* y, int y_stride, const float* gate, int gate_stride, int gate_off, const float* weight,
-                                  int weight_len, int group, int groups, int gate_first, float eps, void* out, int out_is_bf16, int out_stride,
-                                  int tokens, cudaStream_t stream) {
+                                  int weight_len, int group, int groups, int gate_first, float eps, float scale, void* out, int out_is_bf16,
+                                  int out_stride, int tokens, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    if (group <= 0 || groups <= 0 || groups > 65535 || weight_len <= 0) return HB_UNSUPPORTED_SIZE;
+    if (group <= 0 || groups <= 0 || groups > 65535 || (weight && weight_len <= 0)) return HB_UNSUPPORTED_SIZE;
+    if (!weight) weight_len = 1;
     if (group <= 1024) {
         const dim3 warps(tokens, (groups + 3) / 4);
         if (out_is_bf16)
             gated_group_norm_warp_kernel<<<warps, 128, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, groups, gate_first,
-                                                                    eps, (__nv_bfloat16*)out, out_stride);
+                                                                    eps, scale, (__nv_bfloat16*)out, out_stride);
         else
             gated_group_norm_warp_kernel<<<warps, 128, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, groups, gate_first,
-                                                                    eps, (float*)out, out_stride);
+                                                                    eps, scale, (float*)out, out_stride);
         return launch_status();
     }
     const int threads = 256;
     const dim3 grid(tokens, groups);
     if (out_is_bf16)
-        gated_group_norm_kernel<<<grid, threads, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, gate_first, eps,
+        gated_group_norm_kernel<<<grid, threads, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, gate_first, eps, scale,
                                                               (__nv_bfloat16*)out, out_stride);
     else
-        gated_group_norm_kernel<<<grid, threads, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, gate_first, eps,
+        gated_group_norm_kernel<<<grid, threads, 0, stream>>>(y, y_stride, gate, gate_stride, gate_off, weight, weight_len, group, gate_first, eps, scale,
                                                               (float*)out, out_stride);
     return launch_status();
+}
+
+// ---------------------------------------------------------------- the selective scan (a decay per channel and state entry)
+// Per channel c with a state vector S[c, :] of n entries and per token, with a step dt_c = softplus(step input), the channel's
+// input x_c, and two vectors B and C (n entries each) that all channels share:
+//     S[c, i] <- exp(dt_c A[c, i]) S[c, i] + dt_c x_c B_i;     y_c = (sum_i S[c, i] C_i + D_c x_c) * silu(z_c)
+// Channels never meet, so a block of 128 threads walks 32 channels through the tokens of one request's row: four lanes share a
+// channel, each holding n / 4 of its entries in registers (groups of four consecutive entries).  The only chain from token to
+// token is one multiply-add per entry; steps, exponentials and the products with B wait for nothing.  Tokens pass through
+// shared memory in chunks that are fetched while the chunk before is walked.  Sums over n are taken in a fixed order (per lane in
+// four chains, then a butterfly over the four lanes).
+namespace {
+struct SelectiveArgs {
+    const float* x;      // [tokens, x_stride]: the channels' inputs (after the convolution and its activation)
+    int x_stride;
+    const float* dt;     // [tokens, dt_stride]: step inputs per channel (softplus is taken here)
+    int dt_stride;
+    const float* bc;     // [tokens, bc_stride]: B at b_off, C at c_off
+    int bc_stride, b_off, c_off;
+    const float* a;      // [inner, n]: A, negative
+    const float* skip;   // [inner]: D
+    const float* gate;   // [tokens, gate_stride]: z at gate_off
+    int gate_stride, gate_off;
+    float* state;
+    size_t slot_stride;
+    int state_off;
+    const int* slots;
+    const int* row_start;
+    void* out;           // [tokens, out_stride]
+    int out_stride;
+    int inner, n, n_padded;
+};
+
+template <int NG, typename TO>
+__global__ void __launch_bounds__(128) selective_scan_kernel(const SelectiveArgs a) {
+    constexpr int LPC = 4, CH = 128 / LPC, NP = NG * 4 * LPC, CT = NP >= 128 ? 4 : 16;
+    constexpr int NB = CT * NP / 128, NC = CT * CH / 128;
+    __shared__ __align__(16) float sb[2][CT][NP];
+    __shared__ __align__(16) float sc[2][CT][NP];
+    __shared__ float sdt[2][CT][CH], sx[2][CT][CH], sz[2][CT][CH];
+
+    const int row = blockIdx.y, tid = threadIdx.x;
+    const int l = tid % LPC, cw = tid / LPC, channel = blockIdx.x * CH + cw;
+    const bool owns = channel < a.inner;
+    const int t0 = a.row_start[row], t1 = a.row_start[row + 1];
+    float* const kept = a.state + (size_t)a.slots[row] * a.slot_stride + a.state_off + (size_t)channel * a.n_padded;
+
+    float s[NG][4], rate[NG][4];
+#pragma unroll
+    for (int r = 0; r < NG; ++r) {
+        const int base = 4 * (LPC * r + l);
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (owns && base < a.n_padded) v = *reinterpret_cast<const float4*>(kept + base);
+        s[r][0] = v.x; s[r][1] = v.y; s[r][2] = v.z; s[r][3] = v.w;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) rate[r][i] = (owns && base + i < a.n) ? a.a[(size_t)channel * a.n + base + i] : 0.f;
+    }
+    const float skip = owns ? a.skip[channel] : 0.f;
+
+    float pb[NB], pc[NB], pdt[NC], px[NC], pz[NC];
+    auto prefetch = [&](int first) {
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+            const int flat = tid + 128 * i, j = flat / NP, index = flat - j * NP, t = first + j;
+            const bool live = t < t1 && index < a.n;
+            const float* p = a.bc + (size_t)(live ? t : t0) * a.bc_stride;
+            pb[i] = live ? p[a.b_off + index] : 0.f;
+            pc[i] = live ? p[a.c_off + index] : 0.f;
+        }
+#pragma unroll
+        for (int i = 0; i < NC; ++i) {
+            const int flat = tid + 128 * i, j = flat / CH, c = blockIdx.x * CH + (flat - j * CH), t = first + j;
+            const bool live = t < t1 && c < a.inner;
+            pdt[i] = live ? a.dt[(size_t)t * a.dt_stride + c] : 0.f;
+            px[i] = live ? a.x[(size_t)t * a.x_stride + c] : 0.f;
+            pz[i] = live ? a.gate[(size_t)t * a.gate_stride + a.gate_off + c] : 0.f;
+        }
+    };
+    auto publish = [&](int buffer) {
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+            const int flat = tid + 128 * i, j = flat / NP, index = flat - j * NP;
+            sb[buffer][j][index] = pb[i];
+            sc[buffer][j][index] = pc[i];
+        }
+#pragma unroll
+        for (int i = 0; i < NC; ++i) {
+            const int flat = tid + 128 * i, j = flat / CH, c = flat - j * CH;
+            sdt[buffer][j][c] = softplus_f(pdt[i]);
+            sx[buffer][j][c] = px[i];
+            sz[buffer][j][c] = silu_f(pz[i]);
+        }
+    };
+
+    prefetch(t0);
+    publish(0);
+    __syncthreads();
+    int buffer = 0;
+    for (int first = t0; first < t1; first += CT, buffer ^= 1) {
+        const bool more = first + CT < t1;
+        if (more) prefetch(first + CT);  // in flight while this chunk is walked
+        const int count = min(CT, t1 - first);
+        for (int j = 0; j < count; ++j) {
+            const float dt = sdt[buffer][j][cw], xv = sx[buffer][j][cw];
+            const float dx = dt * xv;
+            float part[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int r = 0; r < NG; ++r) {
+                const float4 b4 = *reinterpret_cast<const float4*>(&sb[buffer][j][4 * (LPC * r + l)]);
+                const float4 c4 = *reinterpret_cast<const float4*>(&sc[buffer][j][4 * (LPC * r + l)]);
+                const float bv[4] = {b4.x, b4.y, b4.z, b4.w}, cv[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    s[r][i] = fmaf(expf(dt * rate[r][i]), s[r][i], dx * bv[i]);
+                    part[i] = fmaf(s[r][i], cv[i], part[i]);
+                }
+            }
+            float y = (part[0] + part[1]) + (part[2] + part[3]);
+#pragma unroll
+            for (int offset = 1; offset < LPC; offset <<= 1) y += __shfl_xor_sync(0xffffffffu, y, offset);
+            if (l == 0 && owns) {
+                const float result = fmaf(skip, xv, y) * sz[buffer][j][cw];
+                reinterpret_cast<TO*>(a.out)[(size_t)(first + j) * a.out_stride + channel] = from_float<TO>(result);
+            }
+        }
+        if (!more) break;
+        publish(buffer ^ 1);
+        __syncthreads();
+    }
+#pragma unroll
+    for (int r = 0; r < NG; ++r) {
+        const int base = 4 * (LPC * r + l);
+        if (owns && base < a.n_padded) *reinterpret_cast<float4*>(kept + base) = make_float4(s[r][0], s[r][1], s[r][2], s[r][3]);
+    }
+}
+
+template <typename TO>
+int launch_selective(const SelectiveArgs& a, int rows, cudaStream_t stream) {
+    const int per_lane = (a.n_padded + 15) / 16;  // groups of four entries per lane, four lanes per channel
+    const dim3 grid((a.inner + 31) / 32, rows);
+    if (per_lane <= 1) selective_scan_kernel<1, TO><<<grid, 128, 0, stream>>>(a);
+    else if (per_lane <= 2) selective_scan_kernel<2, TO><<<grid, 128, 0, stream>>>(a);
+    else if (per_lane <= 4) selective_scan_kernel<4, TO><<<grid, 128, 0, stream>>>(a);
+    else if (per_lane <= 8) selective_scan_kernel<8, TO><<<grid, 128, 0, stream>>>(a);
+    else selective_scan_kernel<16, TO><<<grid, 128, 0, stream>>>(a);
+    return launch_status();
+}
+}  // namespace
+
+// The state of (slot, channel) is S[channel, :] in n_padded floats at state + slot * slot_stride + state_off + channel * n_padded; n_padded,
+// state_off and slot_stride are multiples of 4.  `a` holds A itself (negative), not its logarithm.
+HB_EXPORT int hb_selective_scan(const float* x, int x_stride, const float* dt, int dt_stride, const float* bc, int bc_stride, int b_off, int c_off,
+                                const float* a, const float* skip, const float* gate, int gate_stride, int gate_off, float* state,
+                                long long slot_stride, int state_off, const int* slots, const int* row_start, void* out, int out_is_bf16,
+                                int out_stride, int rows, int inner, int n, int n_padded, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (n <= 0 || n > 256 || inner <= 0 || rows > 65535) return HB_UNSUPPORTED_SIZE;
+    if (n_padded < n || (n_padded & 3) || (state_off & 3) || (slot_stride & 3) || (((uintptr_t)state) & 15)) return HB_BAD_ARGUMENT;
+    const SelectiveArgs args{x, x_stride, dt, dt_stride, bc, bc_stride, b_off, c_off, a, skip, gate, gate_stride, gate_off, state, (size_t)slot_stride,
+                             state_off, slots, row_start, out, out_stride, inner, n, n_padded};
+    return out_is_bf16 ? launch_selective<__nv_bfloat16>(args, rows, stream) : launch_selective<float>(args, rows, stream);
 }

@@ -16,6 +16,7 @@ import torch
 from ..engine.batch import PagedView, StateView, StepContext
 from ..parts import base as parts
 from ..parts.base import BuildContext, PagedTokens, RequestState, WeightSpec
+from ..parts.norm import with_offset
 from ..parts.spec import ModelSpec
 
 
@@ -35,6 +36,7 @@ class DecoderModel:
             if layer.arrangement not in parts.ARRANGEMENTS:
                 raise KeyError(f"no arrangement {layer.arrangement!r} is registered")
             self.layers.append(parts.ARRANGEMENTS[layer.arrangement](mixer, feed_forward, norms))
+        self.offsets = parts.make(parts.STREAM_OFFSETS, spec.offsets, self.build) if spec.offsets is not None else None
         self.final_norm = parts.make(parts.NORMS, spec.final_norm, self.build)
         self.head = parts.make(parts.HEADS, spec.head, self.build)
         for index, run in enumerate(spec.schedule):
@@ -51,6 +53,8 @@ class DecoderModel:
                 yield layer_spec.feed_forward.prefix, layer.feed_forward
             for name, norm_spec in layer_spec.norms.items():
                 yield norm_spec.prefix, layer.norms[name]
+        if self.offsets is not None:
+            yield self.spec.offsets.prefix, self.offsets
         yield self.spec.final_norm.prefix, self.final_norm
         yield self.spec.head.prefix, self.head
 
@@ -71,14 +75,17 @@ class DecoderModel:
                 raise ValueError("the head is tied to the embedding, which has no table to share")
             self.head.use_shared_table(table)
 
-    def cache_users(self) -> list[tuple[int, PagedTokens | RequestState]]:
-        """(schedule entry, what its mixer keeps) for every entry that owns a cache."""
+    def cache_users(self) -> list[tuple[object, PagedTokens | RequestState]]:
+        """(user, what it keeps) for every schedule entry that owns a cache: the user is the entry's index, or, for a mixer
+        that keeps several things, (index, which of them)."""
         users = []
         for index, run in enumerate(self.spec.schedule):
             if run.reads_cache_of is not None:
                 continue
             need = self.layers[run.layer].mixer.cache_request()
-            if need is not None:
+            if isinstance(need, tuple):
+                users += [((index, which), one) for which, one in enumerate(need)]
+            elif need is not None:
                 users.append((index, need))
         return users
 
@@ -103,7 +110,13 @@ class DecoderModel:
         delta = None
         for index, run in enumerate(self.spec.schedule):
             owner = index if run.reads_cache_of is None else run.reads_cache_of
-            view = self._cache_view(owner, step, cache)
+            need = self.layers[self.spec.schedule[owner].layer].mixer.cache_request()
+            if isinstance(need, tuple):
+                view = tuple(self._cache_view((owner, which), step, cache) for which in range(len(need)))
+            else:
+                view = self._cache_view(owner, step, cache)
+            if run.offset is not None:
+                delta = with_offset(h, delta, self.offsets.row(run.offset))
             h, delta = self.layers[run.layer].forward(h, delta, step, view, run.reads_cache_of is None)
         if step.n_want == 0:
             # the last pending add is never read: keys and values are already in the cache
@@ -111,7 +124,7 @@ class DecoderModel:
         x = self.final_norm.forward(h, delta, step.want_rows)
         return self.head.forward(x)
 
-    def _cache_view(self, entry: int, step: StepContext, cache):
+    def _cache_view(self, entry, step: StepContext, cache):
         if cache is None or not cache.has_user(entry):
             return None
         kind, group, _ = cache.where(entry)

@@ -234,21 +234,102 @@ def heads_prepare_(x: torch.Tensor, q_heads: int, kv_heads: int, head_dim: int, 
 
 
 def attention_general(q: torch.Tensor, heads: int, kv_heads: int, head_dim: int, v_dim: int, cache: torch.Tensor, block_table: torch.Tensor,
-                      token_row: torch.Tensor, positions: torch.Tensor, page_size: int, scale: float, softcap: float = 0.0, window: int = 0) -> torch.Tensor:
+                      token_row: torch.Tensor, positions: torch.Tensor, page_size: int, scale: float, softcap: float = 0.0, window: int = 0, *,
+                      distance_bias: torch.Tensor | None = None, gate: torch.Tensor | None = None, gate_off: int = 0, out_scale: float = 1.0,
+                      out: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention of every token over its request's pages with keys of ``head_dim`` and values of ``v_dim``, a smooth
-    cap on the scores (0 = none) and a window (0 = all keys); the cache in either arrangement of :func:`paged_strides`."""
-    require_cuda(q, cache, block_table, token_row, positions)
+    cap on the scores (0 = none) and a window (0 = all keys); the cache in either arrangement of :func:`paged_strides`.
+    ``distance_bias`` [heads, span] float: the score of a key ``n`` positions back takes ``distance_bias[head, min(n, span - 1)]``
+    (after scale and cap).  ``gate`` [tokens, *] float: the result is multiplied by ``out_scale * sigmoid(gate[:, gate_off:][token, head * v_dim + i])``.
+    ``out``: a [tokens, >= heads * v_dim] view the result is written to."""
+    require_cuda(q, cache, block_table, token_row, positions, distance_bias, gate, out)
+    for t in (distance_bias, gate):
+        if t is not None and (t.dtype != torch.float32 or t.stride(-1) != 1 or t.dim() != 2):
+            raise KernelError("attention: the distance bias and the gate are float32 matrices with unit inner stride")
+    if distance_bias is not None and (distance_bias.shape[0] != heads or not distance_bias.is_contiguous()):
+        raise KernelError("attention: the distance bias is a dense [heads, span] table")
     if q.dtype != cache.dtype or q.stride(-1) != 1:
         raise KernelError("attention: queries and cache must share their element type")
     v_off, page_stride, head_stride, token_stride = paged_strides(cache, head_dim, v_dim)
     tokens = q.shape[0]
-    out = torch.empty((tokens, heads * v_dim), dtype=q.dtype, device=q.device)
+    if out is None:
+        out = torch.empty((tokens, heads * v_dim), dtype=q.dtype, device=q.device)
+    elif out.dtype != q.dtype or out.shape[0] != tokens or out.shape[1] < heads * v_dim or out.stride(1) != 1:
+        raise KernelError("attention: the output is a [tokens, >= heads * v_dim] view of the queries' element type")
     v_cache = ctypes.c_void_p(cache.data_ptr() + v_off * cache.element_size())
-    check(library("attention_generic").hb_attention_general(
+    check(library("attention_generic").hb_attention_biased(
         ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), i32(is_bf16(q)), ptr(cache), v_cache, ctypes.c_longlong(page_stride),
         ctypes.c_longlong(head_stride), i32(token_stride), ptr(block_table), i32(block_table.shape[1]), ptr(token_row), ptr(positions), i32(tokens),
         i32(heads), i32(kv_heads), i32(head_dim), i32(v_dim), i32(page_size), i32(cache.shape[0]), f32(scale), f32(softcap or 0.0), i32(window or 0),
-        ptr(status_word(q.device)), stream_ptr()), "attention_general")
+        ptr(distance_bias), i32(distance_bias.shape[1] if distance_bias is not None else 0), ptr(gate), i32(gate.stride(0) if gate is not None else 0),
+        i32(gate_off), f32(out_scale), ptr(status_word(q.device)), stream_ptr()), "attention_general")
+    return out
+
+
+def heads_prepare_wide(x: torch.Tensor, q_off: int, k_off: int, v_off: int, q_heads: int, kv_heads: int, head_dim: int, v_dim: int,
+                       positions: torch.Tensor, *, q_out: torch.Tensor, k_out: torch.Tensor | None = None, q_norm: torch.Tensor | None = None,
+                       k_norm: torch.Tensor | None = None, norm_whole: bool = False, eps: float = 0.0, inv_freq: torch.Tensor | None = None,
+                       rot_dims: int = 0, rot_half: bool = False, k_scale: float = 1.0, cache: torch.Tensor | None = None,
+                       block_table: torch.Tensor | None = None, token_row: torch.Tensor | None = None, page_size: int = 0) -> None:
+    """Float projections ``x`` [tokens, *] with queries at column ``q_off``, keys at ``k_off``, values at ``v_off``: query/key
+    norm (per head with one weight, or over the whole projection with a weight per column), rotation (adjacent pairs, or
+    dimension i with i + rot_dims / 2), keys times ``k_scale``; queries to ``q_out`` [tokens, >= q_heads * head_dim], keys and
+    values into ``cache`` (either arrangement of :func:`paged_strides`) or keys to ``k_out`` (values then stay where they are).
+    ``q_out`` and ``k_out`` may be float views of ``x`` itself."""
+    require_cuda(x, positions, q_out, k_out, q_norm, k_norm, inv_freq, cache, block_table, token_row)
+    if x.dtype != torch.float32 or x.stride(-1) != 1 or q_out.stride(-1) != 1 or (k_out is not None and (k_out.stride(-1) != 1 or k_out.dtype != q_out.dtype)):
+        raise KernelError("heads_prepare_wide: float32 projections and outputs with unit inner stride")
+    for t in (q_norm, k_norm, inv_freq):
+        if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+            raise KernelError("heads_prepare_wide: norm weights and frequencies are dense float32")
+    if (cache is None) == (k_out is None):
+        raise KernelError("heads_prepare_wide: keys go either to a cache or to k_out")
+    v_cache_off = page_stride = head_stride = token_stride = pages = 0
+    if cache is not None:
+        if cache.dtype != q_out.dtype:
+            raise KernelError("heads_prepare_wide: queries and cache must share their element type")
+        v_cache_off, page_stride, head_stride, token_stride = paged_strides(cache, head_dim, v_dim)
+        pages = cache.shape[0]
+    v_cache = ctypes.c_void_p(cache.data_ptr() + v_cache_off * cache.element_size()) if cache is not None else ctypes.c_void_p(0)
+    check(library("heads_prepare").hb_heads_prepare_wide(
+        ptr(x), i32(x.shape[0]), i32(x.stride(0)), i32(q_off), i32(k_off), i32(v_off), i32(q_heads), i32(kv_heads), i32(head_dim), i32(v_dim),
+        ptr(q_norm), ptr(k_norm), i32(1 if norm_whole else 0), f32(eps), ptr(inv_freq), i32(rot_dims if inv_freq is not None else 0),
+        i32(1 if rot_half else 0), ptr(positions), f32(k_scale), ptr(q_out), i32(q_out.stride(0)), ptr(k_out),
+        i32(k_out.stride(0) if k_out is not None else 0), i32(is_bf16(q_out)), ptr(cache), v_cache, ctypes.c_longlong(page_stride),
+        ctypes.c_longlong(head_stride), i32(token_stride), ptr(block_table), i32(block_table.shape[1] if block_table is not None else 0),
+        ptr(token_row), i32(page_size), i32(pages), ptr(status_word(x.device)), stream_ptr()), "heads_prepare_wide")
+
+
+def norm_add_norm(h: torch.Tensor, y: torch.Tensor | None, w_post: torch.Tensor | None, eps_post: float, offset: torch.Tensor | None,
+                  w_next: torch.Tensor | None, eps_next: float, out_dtype: torch.dtype, rows: torch.Tensor | None = None) -> torch.Tensor | None:
+    """One launch per sublayer boundary of a block that normalises what a sublayer reads *and* what it returns:
+    ``h += y / rms(y) * w_post (+ offset)`` in the float stream, then ``h / rms(h) * w_next`` returned in ``out_dtype``.
+    Without ``y`` only the offset is added; without ``w_next`` nothing is returned; with ``rows`` (int32 indices) only
+    those rows are worked on and ``h`` stays as it was."""
+    require_cuda(h, y, w_post, offset, w_next, rows)
+    if h.dtype != torch.float32 or not h.is_contiguous() or h.dim() != 2:
+        raise KernelError("norm_add_norm: a dense float32 stream")
+    tokens, hidden = h.shape
+    if y is not None and (y.shape != h.shape or not y.is_contiguous() or w_post is None):
+        raise KernelError("norm_add_norm: a dense sublayer output of the stream's shape with its norm weight")
+    for t in (w_post, offset, w_next):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != hidden or not t.is_contiguous()):
+            raise KernelError("norm_add_norm: weights and the offset are dense float32 vectors of the stream's width")
+    n_rows = rows.numel() if rows is not None else tokens
+    out = torch.empty((n_rows, hidden), dtype=out_dtype, device=h.device) if w_next is not None else None
+    check(library("elementwise").hb_norm_add_norm(ptr(h), ptr(y), i32(is_bf16(y) if y is not None else 0), ptr(w_post), ptr(offset), ptr(w_next), ptr(out),
+                                                  i32(is_bf16(out) if out is not None else 0), ptr(rows), i32(n_rows), i32(hidden), f32(eps_post),
+                                                  f32(eps_next), stream_ptr()), "norm_add_norm")
+    return out
+
+
+def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
+    """0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), computed in float, in the element type of ``x``."""
+    require_cuda(x)
+    if not x.is_contiguous():
+        raise KernelError("gelu_tanh: a dense tensor")
+    out = torch.empty_like(x)
+    check(library("elementwise").hb_gelu_tanh(ptr(x), ptr(out), i32(is_bf16(x)), ctypes.c_longlong(x.numel()), stream_ptr()), "gelu_tanh")
     return out
 
 

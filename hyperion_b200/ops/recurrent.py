@@ -10,7 +10,7 @@ import torch
 
 from .native import KernelError, check, f32, i32, is_bf16, library, ptr, require_cuda, stream_ptr
 
-MODE_DELTA, MODE_STATE_SPACE = 0, 1
+MODE_DELTA, MODE_STATE_SPACE, MODE_RETENTION = 0, 1, 2
 
 
 def _floats(*tensors) -> None:
@@ -57,17 +57,42 @@ def state_scan(mode: int, conv: torch.Tensor, k_off: int, q_off: int, v_off: int
     return out
 
 
-def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, gate_off: int, weight: torch.Tensor, group: int, gate_first: bool, eps: float,
-                     out_dtype: torch.dtype) -> torch.Tensor:
-    """RMS norm of ``y`` [tokens, width] in groups of ``group`` columns, times ``weight`` (indexed by column modulo its length),
-    gated by silu of the columns ``gate_off ..`` of ``gate``: before the norm (``gate_first``) or after it."""
-    require_cuda(y, gate, weight)
+def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, gate_off: int, weight: torch.Tensor | None, group: int, gate_first: bool, eps: float,
+                     out_dtype: torch.dtype, scale: float = 1.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    """RMS norm of ``y`` [tokens, width] in groups of ``group`` columns, times ``weight`` (indexed by column modulo its length;
+    None: no weight), gated by silu of the columns ``gate_off ..`` of ``gate``: before the norm (``gate_first``) or after it,
+    times ``scale``.  ``out``: a [tokens, >= width] view the result is written to."""
+    require_cuda(y, gate, weight, out)
     _floats(y, gate, weight)
     tokens, width = y.shape
     if width % group:
         raise KernelError(f"gated_group_norm: groups of {group} do not divide {width} columns")
-    out = torch.empty((tokens, width), dtype=out_dtype, device=y.device)
+    if out is None:
+        out = torch.empty((tokens, width), dtype=out_dtype, device=y.device)
+    elif out.dtype != out_dtype or out.shape[0] != tokens or out.shape[1] < width or out.stride(1) != 1:
+        raise KernelError("gated_group_norm: the output is a [tokens, >= width] view of the stated type")
     check(library("recurrent").hb_gated_group_norm(ptr(y), i32(y.stride(0)), ptr(gate), i32(gate.stride(0)), i32(gate_off), ptr(weight),
-                                                   i32(weight.numel()), i32(group), i32(width // group), i32(1 if gate_first else 0), f32(eps), ptr(out),
-                                                   i32(is_bf16(out)), i32(out.stride(0)), i32(tokens), stream_ptr()), "gated_group_norm")
+                                                   i32(weight.numel() if weight is not None else 0), i32(group), i32(width // group),
+                                                   i32(1 if gate_first else 0), f32(eps), f32(scale), ptr(out), i32(is_bf16(out)), i32(out.stride(0)),
+                                                   i32(tokens), stream_ptr()), "gated_group_norm")
+    return out
+
+
+def selective_scan(x: torch.Tensor, dt: torch.Tensor, bc: torch.Tensor, b_off: int, c_off: int, a: torch.Tensor, skip: torch.Tensor, gate: torch.Tensor,
+                   gate_off: int, state: torch.Tensor, state_off: int, slots: torch.Tensor, row_start: torch.Tensor, rows: int, n: int, n_padded: int,
+                   out_dtype: torch.dtype) -> torch.Tensor:
+    """The recurrence with a decay per channel and state entry: per channel c, S[c] <- exp(dt_c A[c]) S[c] + dt_c x_c B,
+    y_c = (S[c] . C + D_c x_c) silu(z_c), with dt = softplus(``dt``), B and C the columns ``b_off ..`` and ``c_off ..`` of ``bc``,
+    A = ``a`` [inner, n] (negative), D = ``skip``, z the columns ``gate_off ..`` of ``gate``; every row's tokens walk from and
+    into its slot of ``state``.  Returns [tokens, inner] in ``out_dtype``."""
+    require_cuda(x, dt, bc, a, skip, gate, state, slots, row_start)
+    _floats(x, dt, bc, a, skip, gate, state)
+    tokens, inner = x.shape
+    if a.shape != (inner, n) or not a.is_contiguous() or skip.numel() != inner or dt.shape != x.shape:
+        raise KernelError("selective_scan: A is [inner, n], D [inner], the steps [tokens, inner]")
+    out = torch.empty((tokens, inner), dtype=out_dtype, device=x.device)
+    check(library("recurrent").hb_selective_scan(ptr(x), i32(x.stride(0)), ptr(dt), i32(dt.stride(0)), ptr(bc), i32(bc.stride(0)), i32(b_off), i32(c_off),
+                                                 ptr(a), ptr(skip), ptr(gate), i32(gate.stride(0)), i32(gate_off), ptr(state), ctypes.c_longlong(state.stride(0)),
+                                                 i32(state_off), ptr(slots), ptr(row_start), ptr(out), i32(is_bf16(out)), i32(out.stride(0)), i32(rows),
+                                                 i32(inner), i32(n), i32(n_padded), stream_ptr()), "selective_scan")
     return out

@@ -32,6 +32,7 @@ class WeightSpec:
     shape: tuple[int, ...]
     integer: bool = False  # integer tables are kept as int32, everything else as a float type
     init: str = "normal"  # how random weights fill it: "normal" = N(0, std), "one_plus_normal" = 1 + N(0, std)
+    any_extent: tuple[int, ...] = ()  # dimensions whose extent a checkpoint decides (the part reads it off the tensor); ``shape`` is what random weights get
 
 
 @dataclass(frozen=True)
@@ -125,7 +126,9 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
-    def cache_request(self) -> PagedTokens | RequestState | None:
+    def cache_request(self) -> PagedTokens | RequestState | tuple | None:
+        """What the mixer keeps between steps: nothing, one request, or a tuple of requests (a mixer made of several that
+        each keep something; ``forward`` is then handed a tuple of views in the same order)."""
         return None
 
     def forward(self, x: torch.Tensor, step: Any, cache: Any, own_cache: bool) -> torch.Tensor:
@@ -164,6 +167,12 @@ class Head(Part):
         raise NotImplementedError
 
 
+class StreamOffsets(Part):
+    def row(self, index: int) -> torch.Tensor:
+        """The float vector [hidden] that is added to every row of the stream where the schedule names ``index``."""
+        raise NotImplementedError
+
+
 class Arrangement:
     """How one layer wires its parts.  ``forward`` gets the residual stream ``h`` and a pending
     ``delta`` not yet added to it (so the add fuses with the next norm) and returns the new pair."""
@@ -181,6 +190,7 @@ NORMS: dict[str, Callable[[PartSpec, BuildContext], Norm]] = {}
 POSITIONS: dict[str, Callable[[PartSpec, BuildContext], PositionEncoding]] = {}
 EMBEDDINGS: dict[str, Callable[[PartSpec, BuildContext], Embedding]] = {}
 HEADS: dict[str, Callable[[PartSpec, BuildContext], Head]] = {}
+STREAM_OFFSETS: dict[str, Callable[[PartSpec, BuildContext], StreamOffsets]] = {}
 ARRANGEMENTS: dict[str, Callable[..., Arrangement]] = {}
 
 
@@ -196,6 +206,7 @@ def register_norm(kind: str, factory) -> None: _register(NORMS, kind, factory)
 def register_position(kind: str, factory) -> None: _register(POSITIONS, kind, factory)
 def register_embedding(kind: str, factory) -> None: _register(EMBEDDINGS, kind, factory)
 def register_head(kind: str, factory) -> None: _register(HEADS, kind, factory)
+def register_stream_offsets(kind: str, factory) -> None: _register(STREAM_OFFSETS, kind, factory)
 def register_arrangement(kind: str, factory) -> None: _register(ARRANGEMENTS, kind, factory)
 
 

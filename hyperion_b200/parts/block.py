@@ -36,7 +36,10 @@ class OutputNormBlock(Arrangement):
 
         norm = self.norms["mixer_out"]
         if delta is not None:  # a block before this one left an addition pending
-            h += (delta.tensor() if hasattr(delta, "tensor") else delta).to(h.dtype)
+            if hasattr(delta, "apply"):
+                delta.apply(h)
+            else:
+                h += (delta.tensor() if hasattr(delta, "tensor") else delta).to(h.dtype)
             step.scratch.pop(self.COPY, None)
         if norm.dtype == h.dtype:
             x = h
@@ -52,3 +55,23 @@ class OutputNormBlock(Arrangement):
 
 
 register_arrangement("output_norm", OutputNormBlock)
+
+
+class SandwichNormBlock(Arrangement):
+    """Every sublayer is normalised on both sides: h <- h + norm_b(mixer(norm_a(h))); h <- h + norm_d(feed_forward(norm_c(h))),
+    the second line only when the layer has a feed-forward.  Norm names: ``input``, ``mixer_out``, ``post_mixer``,
+    ``feed_forward_out``.  What a sublayer returns travels on as a :class:`NormedDelta`; the next norm that reads the stream
+    (this layer's, the next layer's or the model's last) normalises it, adds it and normalises the sum in one launch."""
+
+    def forward(self, h, delta, step, cache, own_cache):
+        from .norm import NormedDelta
+
+        x = self.norms["input"].forward(h, delta)
+        pending = NormedDelta(self.mixer.forward(x, step, cache, own_cache), self.norms["mixer_out"])
+        if self.feed_forward is not None:
+            x = self.norms["post_mixer"].forward(h, pending)
+            pending = NormedDelta(self.feed_forward.forward(x, step), self.norms["feed_forward_out"])
+        return h, pending
+
+
+register_arrangement("sandwich_norm", SandwichNormBlock)

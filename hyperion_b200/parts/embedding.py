@@ -6,6 +6,10 @@ float, where head is ``lm_head.weight`` or, with tied embeddings, the embedding 
 Parameters: ``vocab_size``, ``hidden_size``, ``weight_name`` (the tensor's name after the prefix, ``weight``
 unless stated); the embedding also ``scale`` (the looked-up row is multiplied by it in float, 1 unless
 stated); the head also ``tied`` (then it owns no tensor and is handed the embedding's table).
+
+``offset_table`` is a learned table [count, hidden] of vectors that the schedule adds to the stream before an entry
+runs (a model that passes some layers several times marks each pass this way).  Parameters: ``count``, ``hidden_size``,
+``weight_name``.
 """
 from __future__ import annotations
 
@@ -14,7 +18,7 @@ from typing import Mapping
 import torch
 
 from .. import ops
-from .base import BuildContext, Embedding, Head, WeightSpec, register_embedding, register_head
+from .base import BuildContext, Embedding, Head, StreamOffsets, WeightSpec, register_embedding, register_head, register_stream_offsets
 from .spec import PartSpec
 
 
@@ -75,3 +79,23 @@ class LinearHead(Head):
 
 register_embedding("token_embedding", TokenEmbedding)
 register_head("linear_head", LinearHead)
+
+
+class OffsetTable(StreamOffsets):
+    def __init__(self, spec: PartSpec, build: BuildContext):
+        super().__init__(spec, build)
+        self.count = int(spec.params["count"])
+        self.hidden = int(spec.params["hidden_size"])
+        self.weight_name = str(spec.params.get("weight_name", "weight"))
+
+    def weights(self):
+        return {self.weight_name: WeightSpec((self.count, self.hidden))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.table = tensors[self.weight_name].to(torch.float32).contiguous()
+
+    def row(self, index: int) -> torch.Tensor:
+        return self.table[index]
+
+
+register_stream_offsets("offset_table", OffsetTable)

@@ -59,3 +59,34 @@ class SwiGLU(FeedForward):
 
 
 register_feed_forward("swiglu", SwiGLU)
+
+
+class ActivatedMLP(FeedForward):
+    """The feed-forward without a gate: down(act(up(x))), no biases, act = the tanh form of GELU.
+    Parameters: ``hidden_size``, ``intermediate_size``, ``activation`` (``gelu_tanh``), ``names`` (``{"up": ..., "down": ...}``)."""
+
+    def __init__(self, spec: PartSpec, build: BuildContext):
+        super().__init__(spec, build)
+        self.hidden = int(spec.params["hidden_size"])
+        self.inter = int(spec.params["intermediate_size"])
+        self.activation = str(spec.params.get("activation", "gelu_tanh"))
+        if self.activation != "gelu_tanh":
+            raise ValueError(f"no activation {self.activation!r} (known: gelu_tanh)")
+        names = dict(spec.params.get("names") or {})
+        self.up_name, self.down_name = names.get("up", "up_proj.weight"), names.get("down", "down_proj.weight")
+
+    def weights(self) -> dict[str, WeightSpec]:
+        return {self.up_name: WeightSpec((self.inter, self.hidden)), self.down_name: WeightSpec((self.hidden, self.inter))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        self.w_up, self.w_down = tensors[self.up_name].contiguous(), tensors[self.down_name].contiguous()
+
+    def kernel_modules(self):
+        return [("elementwise", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
+
+    def forward(self, x, step):
+        act = ops.gelu_tanh(ops.linear(x, self.w_up, None, self.dtype))
+        return ops.linear(act, self.w_down, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
+
+
+register_feed_forward("activated_mlp", ActivatedMLP)

@@ -4,13 +4,15 @@ y = x * rsqrt(mean(x^2) + eps) * weight, the weight multiplying after the normal
 (helios/crates/helios-hal/kernels/rmsnorm.cu:22-58); the fused form first adds the pending delta into
 the residual stream (rmsnorm.cu:66-122).  The stream, the sum of squares and the products are float;
 the result is rounded once to the activation type.  Parameters: ``hidden_size``, ``eps``, ``weight_name`` (the tensor's
-name after the prefix, ``weight`` unless stated).
+name after the prefix, ``weight`` unless stated), ``one_plus`` (the stored weight lies around zero and one is added to it,
+in float, when it is loaded).
 
 ``add_normed`` is the other placement of the same norm: h <- h + norm(y), for blocks that normalise what a sublayer
 returns instead of what it reads.
 """
 from __future__ import annotations
 
+from dataclasses import dataclass
 from typing import Mapping, Optional
 
 import torch
@@ -20,24 +22,58 @@ from .base import BuildContext, Norm, WeightSpec, register_norm
 from .spec import PartSpec
 
 
+@dataclass
+class NormedDelta:
+    """What a sublayer returned, still to be normalised by ``norm`` (an :class:`RMSNorm`) before it is added to the stream,
+    plus a vector ``offset`` that is added to every row after it.  Either may be absent.  The next norm that reads the stream
+    does all of it in its own launch (``ops.norm_add_norm``)."""
+
+    y: Optional[torch.Tensor]
+    norm: Optional["RMSNorm"]
+    offset: Optional[torch.Tensor] = None
+
+    def apply(self, h: torch.Tensor) -> None:
+        """Do it now, for a reader of the stream that is not a norm."""
+        y = self.y.tensor() if hasattr(self.y, "tensor") else self.y
+        ops.norm_add_norm(h, y, self.norm.weight if y is not None else None, self.norm.eps if y is not None else 0.0, self.offset, None, 0.0, h.dtype)
+
+
+def with_offset(h: torch.Tensor, delta, row: torch.Tensor):
+    """The pending addition ``delta`` (None, a tensor, split-K pieces or a :class:`NormedDelta`) with ``row`` added after it."""
+    if isinstance(delta, NormedDelta):
+        if delta.offset is not None:
+            row = delta.offset + row
+        return NormedDelta(delta.y, delta.norm, row)
+    if delta is not None:
+        h += (delta.tensor() if hasattr(delta, "tensor") else delta).to(h.dtype)
+    return NormedDelta(None, None, row)
+
+
 class RMSNorm(Norm):
     def __init__(self, spec: PartSpec, build: BuildContext):
         super().__init__(spec, build)
         self.hidden = int(spec.params["hidden_size"])
         self.eps = float(spec.params["eps"])
         self.weight_name = str(spec.params.get("weight_name", "weight"))
+        self.one_plus = bool(spec.params.get("one_plus", False))
         self.weight: Optional[torch.Tensor] = None
 
     def weights(self) -> dict[str, WeightSpec]:
-        return {self.weight_name: WeightSpec((self.hidden,), init="one_plus_normal")}
+        return {self.weight_name: WeightSpec((self.hidden,), init="normal" if self.one_plus else "one_plus_normal")}
 
     def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
         self.weight = tensors[self.weight_name].to(torch.float32).contiguous()
+        if self.one_plus:
+            self.weight = (1.0 + self.weight).contiguous()
 
     def kernel_modules(self):
         return [("elementwise", {})]
 
     def forward(self, h, delta, rows=None):
+        if isinstance(delta, NormedDelta):
+            y = delta.y.tensor() if hasattr(delta.y, "tensor") else delta.y
+            return ops.norm_add_norm(h, y, delta.norm.weight if y is not None else None, delta.norm.eps if y is not None else 0.0, delta.offset,
+                                     self.weight, self.eps, self.dtype, rows)
         return ops.add_rmsnorm(h, delta, self.weight, self.eps, self.dtype, rows)
 
     def add_normed(self, h, y):

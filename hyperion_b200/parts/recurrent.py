@@ -21,6 +21,13 @@ State space (``mamba2``), per head with state size n and value size e; the group
     y <- y silu(z), RMS norm in ``norm_groups`` equal parts, times norm, then W_o.
 Parameters: ``hidden_size``, ``heads``, ``value_dim``, ``state``, ``groups``, ``norm_groups``, ``conv`` (taps), ``eps``.
 Tensors: in, conv, conv.b, dt_bias, A_log, D, norm, o.
+
+Selective scan (``mamba1``): the state-space mixer whose decay differs per channel and state entry.  With ``inner`` channels,
+a state of n entries per channel and step inputs of rank r:
+    [x | z] = W_in h;  x <- silu(conv(x) + conv.b);  [d | B | C] = W_x x;  dt = softplus(W_dt d + dt.b), one per channel
+    S[c, i] <- exp(dt_c A[c, i]) S[c, i] + dt_c x_c B_i  with A = -exp(A_log);  y_c = sum_i S[c, i] C_i + D_c x_c
+    y <- y silu(z), then W_o.
+Parameters: ``hidden_size``, ``inner``, ``state``, ``dt_rank``, ``conv`` (taps).  Tensors: in, conv, conv.b, x, dt, dt.b, A_log, D, o.
 """
 from __future__ import annotations
 
@@ -159,5 +166,51 @@ class StateSpaceMixer(_ScanMixer):
         return ops.linear(y, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
 
 
+class SelectiveScanMixer(Mixer):
+    def __init__(self, spec: PartSpec, build: BuildContext):
+        super().__init__(spec, build)
+        p = spec.params
+        self.hidden, self.inner, self.n = int(p["hidden_size"]), int(p["inner"]), int(p["state"])
+        self.rank, self.taps = int(p["dt_rank"]), int(p["conv"])
+        if self.n > 256:
+            raise ValueError(f"a state of {self.n} per channel is above the scan kernel's limit of 256")
+        self.n_padded = _round_up(self.n, 4)
+        self.conv_off = self.inner * self.n_padded  # a multiple of 4: the channels' states come first
+        self.record = _round_up(self.conv_off + (self.taps - 1) * self.inner, 4)
+
+    def weights(self) -> dict[str, WeightSpec]:
+        return {"in": WeightSpec((2 * self.inner, self.hidden)), "conv": WeightSpec((self.inner, self.taps)), "conv.b": WeightSpec((self.inner,)),
+                "x": WeightSpec((self.rank + 2 * self.n, self.inner)), "dt": WeightSpec((self.inner, self.rank)), "dt.b": WeightSpec((self.inner,)),
+                "A_log": WeightSpec((self.inner, self.n)), "D": WeightSpec((self.inner,)), "o": WeightSpec((self.hidden, self.inner))}
+
+    def load(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        f = lambda name: tensors[name].to(torch.float32).contiguous()  # noqa: E731
+        self.w_in, self.w_x, self.w_o = tensors["in"].contiguous(), tensors["x"].contiguous(), tensors["o"].contiguous()
+        self.w_dt, self.b_dt = tensors["dt"].contiguous(), f("dt.b")
+        self.w_conv, self.b_conv = f("conv"), f("conv.b")
+        self.a = (-torch.exp(f("A_log"))).contiguous()
+        self.skip = f("D")
+
+    def cache_request(self):
+        return RequestState((self.record,), torch.float32)
+
+    def kernel_modules(self):
+        return [("recurrent", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
+
+    def forward(self, x, step, cache, own_cache):
+        if cache is None or not own_cache:
+            raise ValueError("the selective scan keeps a state per request; the schedule gave it none")
+        proj = ops.linear(x, self.w_in, None, torch.float32)  # [x | z]
+        state, slots, rows = cache.state, cache.slots, step.n_rows
+        conv = recurrent.causal_conv_silu(proj, 0, self.w_conv, self.b_conv, state, self.conv_off, slots, step.token_row, step.row_start)
+        recurrent.conv_state_update(proj, 0, self.inner, self.taps, state, self.conv_off, slots, step.row_start, rows)
+        dbc = ops.linear(conv, self.w_x, None, torch.float32)  # [d | B | C]
+        dt = ops.linear(dbc[:, : self.rank], self.w_dt, self.b_dt, torch.float32)
+        y = recurrent.selective_scan(conv, dt, dbc, self.rank, self.rank + self.n, self.a, self.skip, proj, self.inner, state, 0, slots,
+                                     step.row_start, rows, self.n, self.n_padded, self.dtype)
+        return ops.linear(y, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
+
+
 register_mixer("delta_rule", GatedDeltaRule)
+register_mixer("mamba1", SelectiveScanMixer)
 register_mixer("mamba2", StateSpaceMixer)

@@ -85,3 +85,23 @@ class InterleavedRotaryEncoding(PositionEncoding):
 
 
 register_position("rope_interleaved", InterleavedRotaryEncoding)
+
+
+class PartialHalfRotaryEncoding(InterleavedRotaryEncoding):
+    """The same without a table for the other pairing: within the first ``dims`` dimensions of a head, dimension i turns
+    together with dimension i + dims/2 by the angle p * base**(-2i/dims) / factor; the rest of the head passes unchanged.
+    It works on float rows (recurrences keep their queries and keys in float).  Parameters: ``dims``, ``base``, ``factor``."""
+
+    half = True
+
+    def apply_(self, x, heads, head_dim, positions):
+        if head_dim < self.dims:
+            raise ValueError(f"rotary encoding of {self.dims} dimensions, used with heads of {head_dim}")
+        if x.dtype != torch.float32:
+            raise ValueError("this rotation works on float rows")
+        width = heads * head_dim
+        ops.heads_prepare_wide(x, 0, 0, 0, heads, 0, head_dim, head_dim, positions, q_out=x[:, :width], k_out=x[:, :width], inv_freq=self.inv_freq,
+                               rot_dims=self.dims, rot_half=True)
+
+
+register_position("rope_half_partial", PartialHalfRotaryEncoding)

@@ -36,10 +36,12 @@ class LayerSpec:
 @dataclass(frozen=True)
 class Run:
     """One entry of the schedule: run ``layer``; its mixer owns a cache of its own unless
-    ``reads_cache_of`` names an earlier schedule entry whose cache it reads instead."""
+    ``reads_cache_of`` names an earlier schedule entry whose cache it reads instead.  ``offset``: the row of the
+    model's table of stream offsets that is added to the stream right before this entry runs."""
 
     layer: int
     reads_cache_of: Optional[int] = None
+    offset: Optional[int] = None
 
 
 @dataclass(frozen=True)
@@ -56,6 +58,8 @@ class ModelSpec:
     # tensor names a checkpoint may carry without their being used (for instance the output matrix
     # of a checkpoint with tied embeddings)
     tolerated: tuple[str, ...] = ()
+    # a table of vectors of the stream's width that schedule entries add to the stream before they run (``Run.offset``)
+    offsets: Optional[PartSpec] = None
 
     def validate(self) -> None:
         for index, run in enumerate(self.schedule):
@@ -66,3 +70,8 @@ class ModelSpec:
                     raise ValueError(f"schedule[{index}] must read the cache of an earlier entry, got {run.reads_cache_of}")
                 if self.schedule[run.reads_cache_of].reads_cache_of is not None:
                     raise ValueError(f"schedule[{index}] reads the cache of an entry that owns none")
+            if run.offset is not None:
+                if self.offsets is None:
+                    raise ValueError(f"schedule[{index}] adds a stream offset, the model has no table of them")
+                if not 0 <= run.offset < int(self.offsets.params["count"]):
+                    raise ValueError(f"schedule[{index}] names offset {run.offset}, the table has {self.offsets.params['count']}")

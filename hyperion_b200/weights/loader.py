@@ -42,7 +42,9 @@ def check_tensors(found: Mapping[str, TensorEntry], expected: Mapping[str, Weigh
     wrong_shape, wrong_type = [], []
     for name in sorted(set(found) & set(expected)):
         entry, wanted = found[name], expected[name]
-        if tuple(entry.shape) != tuple(wanted.shape):
+        free = set(wanted.any_extent)
+        if len(entry.shape) != len(wanted.shape) or any(f != w for i, (f, w) in enumerate(zip(entry.shape, wanted.shape)) if i not in free) \
+                or any(int(entry.shape[i]) < 1 for i in free):
             wrong_shape.append((name, entry.shape, wanted.shape))
         if wanted.integer == entry.dtype.is_floating_point:
             wrong_type.append((name, str(entry.dtype)))
