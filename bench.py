@@ -486,6 +486,166 @@ def nunivik_workload(args) -> int:
     return 0
 
 
+MIROVIK_SIZES = {
+    # width; attention beside retention (heads, kv heads, head size; retention heads, key size, value size); dense feed-forward; experts
+    # (count, per token, inner width, shared inner width); selective scan (channels, state, step rank).  Four layers P+dense, P+experts,
+    # S+dense, P+experts passed twice = eight layer runs, 32,000 tokens
+    "2k": {"width": 2048, "left": (16, 4, 128), "right": (16, 128, 128), "ff": 8192, "experts": (16, 2, 2048, 2048), "selective": (4096, 16, 128)},
+    "4k": {"width": 4096, "left": (32, 8, 128), "right": (32, 128, 128), "ff": 14336, "experts": (16, 2, 3584, 3584), "selective": (8192, 16, 256)},
+}
+
+
+def mirovik_document(size: dict, vocab: int = 32000) -> dict:
+    heads, kv_heads, dim = size["left"]
+    r_heads, r_dim, r_vdim = size["right"]
+    mixer = {"left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "bias_max": 256, "buckets": 32},
+             "right": {"heads": r_heads, "dim": r_dim, "vdim": r_vdim, "decay": [1.0 - 2.0 ** (-5 - 5 * h / max(1, r_heads - 1)) for h in range(r_heads)],
+                       "rot": {"dims": r_dim // 2, "base": 1e6}}, "left_scale": 1.0, "right_scale": 1.0}
+    count, top, inner, shared = size["experts"]
+    dense = {"kind": "dense", "ff": size["ff"]}
+    routed = {"kind": "moe", "router": {"experts": count, "top": top}, "expert": {"ff": inner}, "shared": {"ff": shared}}
+    channels, state, rank = size["selective"]
+    selective = {"inner": channels, "state": state, "dt_rank": rank, "conv": 4}
+    return {"architecture": "Mirovik", "vocab": vocab, "width": size["width"], "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6},
+            "layers": [{"type": "parallel", "mixer": mixer, "mlp": dense}, {"type": "parallel", "mixer": mixer, "mlp": routed},
+                       {"type": "mamba1", "mixer": selective, "mlp": dense}, {"type": "parallel", "mixer": mixer, "mlp": routed}],
+            "loop": {"start": 0, "stop": 4, "times": 2}}
+
+
+def mirovik_kernels(size: dict, measured: dict) -> dict:
+    """The design's own kernels alone at this size, a prompt of 2,048 tokens in one row and 8 rows of one decoded token: time and the bytes each
+    must move against the measured copy bandwidth, for the scans also the float32 operations, for the products of the experts the
+    bfloat16 operations against the measured product rate; beside each the like kernel of the closest model (Nunivik) where there is one."""
+    import torch
+
+    from hyperion_b200 import ops
+    from hyperion_b200.ops import moe, recurrent
+
+    dev = torch.device("cuda")
+    hbm, peak = measured["hbm_gbs"] * 1e9, measured["bf16_tflops"] * 1e12
+    out: dict = {}
+    width = size["width"]
+
+    def rows_of(counts):
+        starts = [0]
+        for c in counts:
+            starts.append(starts[-1] + c)
+        token_row = torch.tensor([r for r, c in enumerate(counts) for _ in range(c)], dtype=torch.int32, device=dev)
+        return torch.tensor(starts, dtype=torch.int32, device=dev), token_row, torch.arange(len(counts), dtype=torch.int32, device=dev)
+
+    def report(name, ms, bytes_moved, fp32_flops=None, bf16_flops=None):
+        entry = {"us": round(ms * 1e3, 2), "bytes": int(bytes_moved), "of_measured_bandwidth": round(bytes_moved / (ms / 1e3) / hbm, 3)}
+        if fp32_flops is not None:
+            entry["fp32_tflops"] = round(fp32_flops / (ms / 1e3) / 1e12, 2)
+        if bf16_flops is not None:
+            entry["of_measured_bf16_rate"] = round(bf16_flops / (ms / 1e3) / peak, 3)
+        out[name] = entry
+
+    for shape, counts in (("prefill_2048", [PROMPT]), ("decode_8", [1] * 8)):
+        tokens = sum(counts)
+        row_start, token_row, slots = rows_of(counts)
+        positions = torch.cat([torch.arange(c, dtype=torch.int32) + (0 if c > 1 else PROMPT) for c in counts]).to(dev)
+        h = torch.randn(tokens, width, device=dev)
+        y = torch.randn(tokens, width, device=dev).to(torch.bfloat16)
+        weight = torch.ones(width, device=dev)
+        report(f"norm_add_norm/{shape}", timed(lambda: ops.norm_add_norm(h, y, weight, 1e-6, None, weight, 1e-6, torch.bfloat16)), tokens * width * (4 + 4 + 2 + 2))
+        report(f"nunivik.rmsnorm_add/{shape}", timed(lambda: ops.rmsnorm_add(h, y, weight, 1e-6, copy_dtype=torch.bfloat16)), tokens * width * (4 + 4 + 2 + 2))
+        # retention: rotation of queries and keys in place, the scan, the gated unit norm
+        heads, n, e = size["right"]
+        proj = torch.randn(tokens, 2 * heads * n + 2 * heads * e, device=dev) * 0.5
+        inv_freq = torch.rand(n // 4, device=dev)
+        k_off, v_off, g_off = heads * n, 2 * heads * n, 2 * heads * n + heads * e
+        report(f"retention.rotate/{shape}", timed(lambda: ops.heads_prepare_wide(proj, 0, k_off, v_off, heads, heads, n, e, positions, q_out=proj[:, :k_off],
+                                                                              k_out=proj[:, k_off:v_off], inv_freq=inv_freq, rot_dims=n // 2, rot_half=True,
+                                                                              k_scale=1.0)), tokens * 2 * heads * n * 8)
+        decay = torch.full((heads,), 0.99, device=dev)
+        state = torch.zeros(len(counts), heads * e * n, device=dev)
+        scan = lambda: recurrent.state_scan(recurrent.MODE_RETENTION, proj, k_off, 0, v_off, proj, 0, 0, decay, decay, None, state, 0, slots, row_start,
+                                            len(counts), heads, heads, n, n, e)
+        report(f"retention.scan/{shape}", timed(scan), 4 * (tokens * (2 * heads * n + 2 * heads * e) + 2 * len(counts) * heads * e * n), fp32_flops=4.0 * tokens * heads * n * e)
+        o = scan()
+        gated = torch.empty(tokens, heads * e, dtype=torch.bfloat16, device=dev)
+        report(f"retention.gated_norm/{shape}", timed(lambda: recurrent.gated_group_norm(o, proj, g_off, None, e, False, 1e-6, torch.bfloat16, out=gated)),
+               tokens * heads * e * (4 + 4 + 2))
+        # the like kernel of the closest model: its state-space scan at the same state size
+        ones, zeros = torch.ones(heads, device=dev), torch.zeros(heads, device=dev)
+        like = lambda: recurrent.state_scan(recurrent.MODE_STATE_SPACE, proj, k_off, 0, v_off, proj, g_off, g_off, zeros, zeros, ones, state, 0, slots, row_start,
+                                            len(counts), heads, heads, n, n, e)
+        report(f"nunivik.state_space_scan/{shape}", timed(like), 4 * (tokens * (2 * heads * n + 2 * heads * e) + 2 * len(counts) * heads * e * n),
+               fp32_flops=4.0 * tokens * heads * n * e)
+        # selective scan
+        channels, states, rank = size["selective"]
+        x = torch.randn(tokens, channels, device=dev) * 0.5
+        dt = torch.randn(tokens, channels, device=dev) - 2.0
+        bc = torch.randn(tokens, rank + 2 * states, device=dev)
+        gate = torch.randn(tokens, 2 * channels, device=dev)
+        a = -torch.rand(channels, states, device=dev) - 0.5
+        skip = torch.ones(channels, device=dev)
+        s_state = torch.zeros(len(counts), channels * states, device=dev)
+        report(f"selective.scan/{shape}", timed(lambda: recurrent.selective_scan(x, dt, bc, rank, rank + states, a, skip, gate, channels, s_state, 0, slots, row_start,
+                                                                                 len(counts), states, states, torch.bfloat16)),
+               4 * (tokens * (3 * channels + 2 * states) + 2 * len(counts) * channels * states) + 2 * tokens * channels, fp32_flops=6.0 * tokens * channels * states)
+        w_conv, b_conv = torch.randn(channels, 4, device=dev) * 0.3, torch.zeros(channels, device=dev)
+        c_state = torch.zeros(len(counts), 3 * channels, device=dev)
+        report(f"selective.conv/{shape}", timed(lambda: recurrent.causal_conv_silu(gate, 0, w_conv, b_conv, c_state, 0, slots, token_row, row_start)), tokens * channels * 8)
+        # routed experts: router, plan, gather, the two grouped products, the sum
+        count, top, inner, _ = size["experts"]
+        xb = (torch.randn(tokens, width, device=dev)).to(torch.bfloat16)
+        router = torch.randn(count, width, device=dev) * 0.05
+        w_gu = (torch.randn(count, 2 * inner, width, device=dev) * 0.02).to(torch.bfloat16)
+        w_down = (torch.randn(count, width, inner, device=dev) * 0.02).to(torch.bfloat16)
+        report(f"experts.route/{shape}", timed(lambda: moe.route(xb, router, top)), tokens * width * 2 + count * width * 4)
+        chosen, weights = moe.route(xb, router, top)
+        report(f"experts.plan/{shape}", timed(lambda: moe.plan(chosen, weights, count)), tokens * top * 16)
+        where = moe.plan(chosen, weights, count)
+        report(f"experts.gather/{shape}", timed(lambda: moe.gather(xb, where)), tokens * top * width * 4)
+        rows = moe.gather(xb, where)
+        used = min(count, tokens * top)  # experts whose matrices are read at all
+        report(f"experts.gate_up_product/{shape}", timed(lambda: moe.grouped_linear(rows, w_gu, where)), used * 2 * inner * width * 2 + tokens * top * (width + 2 * inner) * 2,
+               bf16_flops=2.0 * tokens * top * 2 * inner * width)
+        act = ops.swiglu(moe.grouped_linear(rows, w_gu, where))
+        report(f"experts.down_product/{shape}", timed(lambda: moe.grouped_linear(act, w_down, where)), used * inner * width * 2 + tokens * top * (width + inner) * 2,
+               bf16_flops=2.0 * tokens * top * inner * width)
+        z = moe.grouped_linear(act, w_down, where)
+        report(f"experts.combine/{shape}", timed(lambda: moe.combine(z, where, xb, tokens)), tokens * (top + 2) * width * 2)
+        # the like kernel of the closest model: one dense product of as many operations (a feed-forward's up projection over top * inner columns)
+        dense_w = (torch.randn(top * 2 * inner, width, device=dev) * 0.02).to(torch.bfloat16)
+        report(f"nunivik.dense_product/{shape}", timed(lambda: ops.linear(xb, dense_w, None, torch.bfloat16)), top * 2 * inner * width * 2 + tokens * (width + top * 2 * inner) * 2,
+               bf16_flops=2.0 * tokens * top * 2 * inner * width)
+    return out
+
+
+def mirovik_workload(args) -> int:
+    """Prefill (one prompt of 2,048 tokens in one step) and decode (batch 8 from a context of 2,048) of the Mirovik design at two sizes that
+    resemble real layers, beside the closest model of the package, Nunivik, at equal width, heads, feed-forward and number of layer runs;
+    random weights."""
+    import torch
+
+    from hyperion_b200.api import Engine
+    from hyperion_b200.config import MirovikConfig, NunivikConfig
+
+    measured, kind = peaks()
+    for name, size in MIROVIK_SIZES.items():
+        if args.size and name != args.size:
+            continue
+        arms = {"mirovik": ("Mirovik", MirovikConfig.from_dict(mirovik_document(size))),
+                "nunivik": ("Nunivik", NunivikConfig.from_dict(nunivik_document(NUNIVIK_SIZES[name])))}
+        line = {"workload": "mirovik", "size": name, "dtype": "bf16", "data": "synthetic: random weights and token ids",
+                "layers": "(P+dense P+experts S+dense P+experts) x 2 beside A A D S A A D S", "peaks": kind}
+        for arm, (architecture, config) in arms.items():
+            engine = Engine.from_random(architecture, config, seed=0, dtype="bfloat16", page_size=16, max_tokens=8 * (PROMPT + 256), max_requests=8)
+            prefill = time_prefill(engine)
+            decode = time_decode(engine, 8, 16, max(3, args.warmup), decode_tokens=max(3, args.warmup) + 160)
+            line[arm] = {"prefill_ms": round(prefill["ms"], 3), "prefill_tokens_per_s": round(PROMPT / prefill["ms"] * 1e3),
+                         "decode_ms_per_step": round(decode["ms_per_step"], 4), "decode_tokens_per_s": round(decode["tok_s"], 1),
+                         "decode_launches_per_step": round(decode["launches"] / decode["steps"], 1)}
+            del engine
+            torch.cuda.empty_cache()
+        line["kernels"] = mirovik_kernels(size, measured)
+        print(json.dumps(line))
+    return 0
+
+
 def main() -> int:
     parser = argparse.ArgumentParser()
     parser.add_argument("--gpus", type=int, default=1)
@@ -498,12 +658,13 @@ def main() -> int:
     parser.add_argument("--impl", default="ours", choices=["ours", "reference"])
     parser.add_argument("--skip-points", action="store_true", help="leave out the batch 1 / 64 points, prefill and e2e")
     parser.add_argument("--only", default=None, choices=["prefill"], help="time one part alone (for profiling)")
-    parser.add_argument("--workload", default=None, choices=["mixed-1.5b", "batch-32b", "reference-tables", "nunivik"],
+    parser.add_argument("--workload", default=None, choices=["mixed-1.5b", "batch-32b", "reference-tables", "nunivik", "mirovik"],
                         help="one of the other workloads instead: 128 requests with prompts of 16..4096 tokens and 256 decoded tokens "
                              "each through generate() at the 1.5B shape; batch 16 with prompts of 4,096 and 512 decoded tokens at the 32B shape; "
                              "or the reference's own published tables (decode by batch at context 512, prefill by length) at the 0.5B and 7B shapes; "
-                             "or the Nunivik design at two layer sizes beside the Qwen2 model of equal size, with its own kernels timed alone")
-    parser.add_argument("--size", default=None, choices=["2k", "4k"], help="with --workload nunivik: one of its sizes only")
+                             "or the Nunivik design at two layer sizes beside the Qwen2 model of equal size, with its own kernels timed alone; "
+                             "or the Mirovik design at two layer sizes beside the Nunivik model of equal size, likewise")
+    parser.add_argument("--size", default=None, choices=["2k", "4k"], help="with --workload nunivik or mirovik: one of its sizes only")
     args = parser.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -511,6 +672,8 @@ def main() -> int:
         return reference_tables()
     if args.workload == "nunivik":
         return nunivik_workload(args)
+    if args.workload == "mirovik":
+        return mirovik_workload(args)
     if args.workload:
         return other_workload(args.workload)
     if args.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:

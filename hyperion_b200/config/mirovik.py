@@ -181,6 +181,13 @@ class MirovikConfig:
         return document
 
 
+def _number(document: Any, path: str, key: str) -> float:
+    value = _get(document, path, key)
+    if isinstance(value, bool) or not isinstance(value, (int, float)) or value != value or value in (float("inf"), float("-inf")):
+        raise ConfigError(f"{path}{key}", f"must be a finite number, got {value!r}")
+    return float(value)
+
+
 def _parallel(m: Any, path: str) -> ParallelMixer:
     left, right = _get(m, path, "left"), _get(m, path, "right")
     lp, rp = path + "left.", path + "right."
@@ -203,7 +210,7 @@ def _parallel(m: Any, path: str) -> ParallelMixer:
         rot_base = _positive_number(rot, rp + "rot.", "base")
     retention = RetentionSizes(heads=r_heads, dim=dim, vdim=_positive_int(right, rp, "vdim"), decay=tuple(float(d) for d in decay),
                                rot_dims=rot_dims, rot_base=rot_base)
-    return ParallelMixer(attention, retention, _positive_number(m, path, "left_scale"), _positive_number(m, path, "right_scale"))
+    return ParallelMixer(attention, retention, _number(m, path, "left_scale"), _number(m, path, "right_scale"))
 
 
 def _mlp(mlp: Any, path: str):

@@ -215,6 +215,9 @@ struct AttnArgs {
     int* status;
     int wide_stores;  // rows of the output start on 32-byte boundaries
     float cap_pre, cap_post;  // scale / cap and cap * log2(e) of a smooth cap on the scores (then scale_log2 is 1); cap_pre 0: none
+    const float* bias;  // [heads, bias_span] floats times log2(e), or null: a key n positions back adds bias[head, min(n, bias_span - 1)] to its score
+    int bias_span;
+    float bias_to_raw;  // 1 / scale_log2: a bias is added to the raw score as bias * bias_to_raw, so that the one scaling that follows stands
 };
 
 // tiles[3*i] = first token (flat index), tiles[3*i+1] = token count, tiles[3*i+2] = batch row; virtual row v of a tile is
@@ -227,6 +230,7 @@ struct AttnArgs {
 // tile all of them; with one block per item the longest item alone would set the kernel's time, now the items spread
 // evenly over the blocks. `work` = {items handed out beyond every block's first, blocks that have finished}: the block
 // that finishes last sets both back to zero for the next launch in the stream.
+template <bool BIASED>  // a bias by distance on the scores: a kernel of its own, so that the other keeps its registers
 __global__ void __launch_bounds__(THREADS, 1) attention_tc_kernel(const __grid_constant__ CUtensorMap kv_map, const __grid_constant__ CUtensorMap q_map,
                                                                   const AttnArgs a,
                                                                   const int* __restrict__ tiles, int n_work_tiles, int ys, int gc, int head_chunks,
@@ -508,6 +512,20 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc_kernel(const __grid_c
                         for (int i = 0; i < BN; ++i) s[i] = capped_score_log2(s[i], a.cap_pre, a.cap_post);
                     }
                     const int tile_base = it.start + j * BN;
+                    // A bias by distance: from bias_span - 1 positions back it is one value per head.  A tile that lies that far
+                    // behind every row of the warp takes it as a shift of the whole tile (nothing per score); only the tiles
+                    // near the diagonal look their scores' biases up.
+                    float shift = 0.f;
+                    if (BIASED) {
+                        const float* mine = a.bias + (size_t)(it.first_head + (row_valid ? hh : 0)) * a.bias_span;
+                        const int nearest = hi - (tile_base + BN - 1);  // the distance of the tile's last key
+                        if (__all_sync(0xffffffffu, nearest >= a.bias_span - 1)) {
+                            shift = mine[a.bias_span - 1];
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < BN; ++i) s[i] = fmaf(__ldg(mine + min(max(hi - tile_base - i, 0), a.bias_span - 1)), a.bias_to_raw, s[i]);
+                        }
+                    }
                     // one way for the whole warp: the masked walk only where some row of the warp needs it
                     const int last_visible = hi - tile_base, first_visible = lo - tile_base;  // among the tile's keys 0 .. BN - 1
                     if (!__all_sync(0xffffffffu, last_visible >= BN - 1 && first_visible <= 0)) {
@@ -517,7 +535,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc_kernel(const __grid_c
                     float part[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
                     for (int i = 0; i < BN; ++i) part[i & 3] = fmaxf(part[i & 3], s[i]);
-                    const float tmax = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])) * scale;  // the scale is positive: the largest score stays the largest
+                    const float tmax = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3])) * scale + shift;  // the scale is positive: the largest score stays the largest
                     const float m_new = fmaxf(m, tmax);
                     float alpha = 1.f;
                     if (m == -INFINITY) {
@@ -526,7 +544,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_tc_kernel(const __grid_c
                         alpha = exp2f(m - m_new);
                         m = m_new;
                     }
-                    const float minus_m = (m == -INFINITY) ? 0.f : -m;
+                    const float minus_m = ((m == -INFINITY) ? 0.f : -m) + shift;
                     float sum[4] = {0.f, 0.f, 0.f, 0.f};
                     unsigned words[BN / 2];
 #pragma unroll
@@ -641,12 +659,14 @@ constexpr size_t SMEM_BYTES = SMEM_USED > 120 * 1024 ? SMEM_USED : 120 * 1024;
 // 256 / min(group, 256) tokens.
 HB_EXPORT int hb_attention_tc_tile_rows() { return ROWS; }
 
-HB_EXPORT int hb_attention_tc_tiles_capped(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+// bias [heads, bias_span] float (optional), already times log2(e): see AttnArgs.  Not together with a cap.
+HB_EXPORT int hb_attention_tc_tiles_biased(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
                                     int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int n_tokens,
-                                    int heads, int kv_heads, int head_dim, int page_size, int pages, float scale, float softcap, int window, int* status,
-                                    int* work, cudaStream_t stream) {
+                                    int heads, int kv_heads, int head_dim, int page_size, int pages, float scale, float softcap, int window,
+                                    const float* bias, int bias_span, int* status, int* work, cudaStream_t stream) {
     (void)token_row;
     if (!work) return HB_BAD_ARGUMENT;
+    if (bias && (bias_span <= 0 || softcap > 0.f)) return HB_BAD_ARGUMENT;
     if (n_tiles <= 0) return 0;
     if (n_tokens <= 0) return HB_BAD_ARGUMENT;
     if (head_dim != D) return HB_UNSUPPORTED_SIZE;
@@ -676,11 +696,13 @@ HB_EXPORT int hb_attention_tc_tiles_capped(const void* q, int q_stride, void* ou
         return HB_BAD_ARGUMENT;
     AttnArgs a{(const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_width, positions,
                heads, kv_heads, page_size, pages, window, softcap > 0.f ? 1.f : scale * 1.4426950408889634f, status,
-               (((uintptr_t)out & 31) == 0 && out_stride % 16 == 0) ? 1 : 0, softcap > 0.f ? scale / softcap : 0.f, softcap * 1.4426950408889634f};
+               (((uintptr_t)out & 31) == 0 && out_stride % 16 == 0) ? 1 : 0, softcap > 0.f ? scale / softcap : 0.f, softcap * 1.4426950408889634f,
+               bias, bias_span, 1.f / (scale * 1.4426950408889634f)};
     if ((long long)kv_heads * head_chunks > 65535) return HB_UNSUPPORTED_SIZE;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_tc_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
@@ -691,8 +713,19 @@ HB_EXPORT int hb_attention_tc_tiles_capped(const void* q, int q_stride, void* ou
     const long long items = (long long)n_tiles * kv_heads * head_chunks;
     if (items > 0x7fffffffLL) return HB_UNSUPPORTED_SIZE;
     const int blocks = (int)(items < (long long)sms ? items : (long long)sms);
-    return launch_after_previous(attention_tc_kernel, dim3(blocks), THREADS, SMEM_BYTES, stream, map, q_map, a, tiles, n_tiles, kv_heads * head_chunks, gc,
+    if (bias)
+        return launch_after_previous(attention_tc_kernel<true>, dim3(blocks), THREADS, SMEM_BYTES, stream, map, q_map, a, tiles, n_tiles,
+                                     kv_heads * head_chunks, gc, head_chunks, work);
+    return launch_after_previous(attention_tc_kernel<false>, dim3(blocks), THREADS, SMEM_BYTES, stream, map, q_map, a, tiles, n_tiles, kv_heads * head_chunks, gc,
                                  head_chunks, work);
+}
+
+HB_EXPORT int hb_attention_tc_tiles_capped(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+                                    int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int n_tokens,
+                                    int heads, int kv_heads, int head_dim, int page_size, int pages, float scale, float softcap, int window, int* status,
+                                    int* work, cudaStream_t stream) {
+    return hb_attention_tc_tiles_biased(q, q_stride, out, out_stride, cache, block_table, table_width, token_row, positions, tiles, n_tiles, n_tokens, heads,
+                                        kv_heads, head_dim, page_size, pages, scale, softcap, window, nullptr, 0, status, work, stream);
 }
 
 HB_EXPORT int hb_attention_tc_tiles(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,

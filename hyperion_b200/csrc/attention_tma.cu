@@ -101,7 +101,8 @@ struct RowState {
 // One warp: 16 query rows (padded tile `qs`) against NT * 8 keys starting at key `key0` of the swizzled K / V tiles.
 template <int NT>
 __device__ __forceinline__ void process_keys(RowState& st, const bf16* qs, const bf16* ks, const bf16* vs, int key0, int base,
-                                             const int (&hi)[2], const int (&lo)[2], float scale_log2, float cap_pre, float cap_post) {
+                                             const int (&hi)[2], const int (&lo)[2], float scale_log2, float cap_pre, float cap_post,
+                                             const float* const (&bias)[2], int bias_span) {
     const int lane = threadIdx.x & 31, m = lane >> 3;
     float s[NT][4];
 #pragma unroll
@@ -125,7 +126,11 @@ __device__ __forceinline__ void process_keys(RowState& st, const bf16* qs, const
         for (int e = 0; e < 4; ++e) {
             const int r = e >> 1;
             const int pos = base + key0 + n * 8 + (lane & 3) * 2 + (e & 1);
-            const float v = (pos <= hi[r] && pos >= lo[r]) ? (cap_pre > 0.f ? capped_score_log2(s[n][e], cap_pre, cap_post) : s[n][e] * scale_log2) : -INFINITY;
+            float v = -INFINITY;
+            if (pos <= hi[r] && pos >= lo[r]) {
+                v = cap_pre > 0.f ? capped_score_log2(s[n][e], cap_pre, cap_post) : s[n][e] * scale_log2;
+                if (bias[r]) v += bias[r][min(hi[r] - pos, bias_span - 1)];
+            }
             s[n][e] = v;
             mx[r] = fmaxf(mx[r], v);
         }
@@ -184,6 +189,8 @@ struct AttnArgs {
     float scale_log2;
     int* status;
     float cap_pre, cap_post;  // scale / cap and cap * log2(e) of a smooth cap on the scores; cap_pre 0: none
+    const float* bias;  // [heads, bias_span] floats times log2(e), or null: a key n positions back adds bias[head, min(n, bias_span - 1)] to its score
+    int bias_span;
 };
 
 __host__ __device__ constexpr int stages_for(bool tokens) { return D <= 64 ? 4 : (tokens && D <= 128 ? 3 : 2); }
@@ -341,6 +348,7 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
     }
     // ---------------------------------------------------------------------- consumers
     int hi[2], lo[2];
+    const float* bias[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int v = (TOKENS ? 0 : warp * 16) + (lane >> 2) + r * 8;
@@ -348,6 +356,7 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
         const bool valid = tok < ntok && hh < heads_here;
         hi[r] = valid ? pos_first + tok : -1;
         lo[r] = (valid && a.window > 0) ? max(0, hi[r] - a.window + 1) : 0;
+        bias[r] = (valid && a.bias) ? a.bias + (size_t)(first_head + hh) * a.bias_span : nullptr;
     }
     const int warp_first_tok = TOKENS ? 0 : (warp * 16) / gc;
     const int warp_hi = pos_first + (TOKENS ? 0 : min(ntok - 1, (warp * 16 + 15) / gc));
@@ -362,10 +371,10 @@ __global__ void __launch_bounds__(THREADS) attention_tma_kernel(const __grid_con
         const bf16* ks = reinterpret_cast<const bf16*>(ring + (size_t)s * STAGE_BYTES);
         const int base = start + it * BN;
         if (TOKENS) {
-            if (base + warp * 16 <= pos_last) process_keys<2>(st, qs, ks, ks + TILE_ELEMS, warp * 16, base, hi, lo, a.scale_log2, a.cap_pre, a.cap_post);
+            if (base + warp * 16 <= pos_last) process_keys<2>(st, qs, ks, ks + TILE_ELEMS, warp * 16, base, hi, lo, a.scale_log2, a.cap_pre, a.cap_post, bias, a.bias_span);
         } else if (!TOKENS) {
             if (warp_has_rows && base <= warp_hi && base + BN - 1 >= warp_lo)
-                process_keys<BN / 8>(st, qs + warp * 16 * LDQ, ks, ks + TILE_ELEMS, 0, base, hi, lo, a.scale_log2, a.cap_pre, a.cap_post);
+                process_keys<BN / 8>(st, qs + warp * 16 * LDQ, ks, ks + TILE_ELEMS, 0, base, hi, lo, a.scale_log2, a.cap_pre, a.cap_post, bias, a.bias_span);
         }
         __syncwarp();
         if (lane == 0) mbar_arrive(&empty[s]);
@@ -493,8 +502,9 @@ constexpr size_t smem_bytes() {
 // The cache layer as a matrix [pages * 2 * kv_heads * page_size, D] fetched in boxes of page_size rows x 64 columns.
 int prepare(CUtensorMap* map, AttnArgs& a, const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
             int table_width, const int* token_row, const int* positions, int heads, int kv_heads, int head_dim, int page_size, int pages,
-            float scale, float softcap, int window, int* status) {
+            float scale, float softcap, int window, const float* bias, int bias_span, int* status) {
     if (head_dim != D) return HB_UNSUPPORTED_SIZE;
+    if (bias && bias_span <= 0) return HB_BAD_ARGUMENT;
     if (kv_heads <= 0 || heads % kv_heads || q_stride % 8 || out_stride % 2) return HB_BAD_ARGUMENT;
     if (page_size < 8 || page_size > 64 || (page_size & (page_size - 1))) return HB_UNSUPPORTED_SIZE;
     if (((uintptr_t)q | (uintptr_t)cache) & 15) return HB_BAD_ARGUMENT;
@@ -509,20 +519,21 @@ int prepare(CUtensorMap* map, AttnArgs& a, const void* q, int q_stride, void* ou
         return HB_BAD_ARGUMENT;
     a = AttnArgs{(const bf16*)q, q_stride, (bf16*)out, out_stride, block_table, table_width, token_row, positions,
                  heads, kv_heads, page_size, pages, window, scale * 1.4426950408889634f, status,
-                 softcap > 0.f ? scale / softcap : 0.f, softcap * 1.4426950408889634f};
+                 softcap > 0.f ? scale / softcap : 0.f, softcap * 1.4426950408889634f, bias, bias_span};
     return 0;
 }
 }  // namespace
 
-HB_EXPORT int hb_attention_tma_tiles_capped(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+// bias [heads, bias_span] float (optional), already times log2(e): a key n positions back adds bias[head, min(n, bias_span - 1)] to its score.
+HB_EXPORT int hb_attention_tma_tiles_biased(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
                                      int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int heads,
-                                     int kv_heads, int head_dim, int page_size, int pages, float scale, float softcap, int window, int* status,
-                                     cudaStream_t stream) {
+                                     int kv_heads, int head_dim, int page_size, int pages, float scale, float softcap, int window,
+                                     const float* bias, int bias_span, int* status, cudaStream_t stream) {
     if (n_tiles <= 0) return 0;
     CUtensorMap map;
     AttnArgs a;
     if (int code = prepare(&map, a, q, q_stride, out, out_stride, cache, block_table, table_width, token_row, positions, heads, kv_heads,
-                           head_dim, page_size, pages, scale, softcap, window, status)) return code;
+                           head_dim, page_size, pages, scale, softcap, window, bias, bias_span, status)) return code;
     const int group = heads / kv_heads, gc = group < 64 ? group : 64, head_chunks = (group + gc - 1) / gc;
     if ((long long)kv_heads * head_chunks > 65535) return HB_UNSUPPORTED_SIZE;
     static bool configured = false;
@@ -535,6 +546,14 @@ HB_EXPORT int hb_attention_tma_tiles_capped(const void* q, int q_stride, void* o
                                  gc, head_chunks, 1, nullptr, nullptr);
 }
 
+HB_EXPORT int hb_attention_tma_tiles_capped(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+                                     int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int heads,
+                                     int kv_heads, int head_dim, int page_size, int pages, float scale, float softcap, int window, int* status,
+                                     cudaStream_t stream) {
+    return hb_attention_tma_tiles_biased(q, q_stride, out, out_stride, cache, block_table, table_width, token_row, positions, tiles, n_tiles, heads, kv_heads,
+                                         head_dim, page_size, pages, scale, softcap, window, nullptr, 0, status, stream);
+}
+
 HB_EXPORT int hb_attention_tma_tiles(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
                                      int table_width, const int* token_row, const int* positions, const int* tiles, int n_tiles, int heads,
                                      int kv_heads, int head_dim, int page_size, int pages, float scale, int window, int* status,
@@ -542,15 +561,15 @@ HB_EXPORT int hb_attention_tma_tiles(const void* q, int q_stride, void* out, int
     return hb_attention_tma_tiles_capped(q, q_stride, out, out_stride, cache, block_table, table_width, token_row, positions, tiles, n_tiles, heads, kv_heads, head_dim, page_size, pages, scale, 0.f, window, status, stream);
 }
 
-HB_EXPORT int hb_attention_tma_tokens_capped(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+HB_EXPORT int hb_attention_tma_tokens_biased(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
                                       int table_width, const int* token_row, const int* positions, const int* items, int n_items, int splits,
                                       float* workspace, int heads, int kv_heads, int head_dim, int page_size, int pages, float scale, float softcap,
-                                      int window, int* status, cudaStream_t stream) {
+                                      int window, const float* bias, int bias_span, int* status, cudaStream_t stream) {
     if (n_items <= 0) return 0;
     CUtensorMap map;
     AttnArgs a;
     if (int code = prepare(&map, a, q, q_stride, out, out_stride, cache, block_table, table_width, token_row, positions, heads, kv_heads,
-                           head_dim, page_size, pages, scale, softcap, window, status)) return code;
+                           head_dim, page_size, pages, scale, softcap, window, bias, bias_span, status)) return code;
     const int group = heads / kv_heads, head_chunks = (group + 15) / 16;
     if (splits < 1 || splits > 65535 || (long long)kv_heads * head_chunks > 65535 || (splits > 1 && !workspace)) return HB_BAD_ARGUMENT;
     static bool configured = false;
@@ -566,6 +585,14 @@ HB_EXPORT int hb_attention_tma_tokens_capped(const void* q, int q_stride, void* 
     if (code || splits == 1) return code;
     return launch_after_previous(attention_merge_kernel, dim3(n_items, heads), D < 128 ? 64 : 128, 0, stream, items, (const float*)ws_o,
                                  (const float*)ws_ml, (bf16*)out, out_stride, heads, splits);
+}
+
+HB_EXPORT int hb_attention_tma_tokens_capped(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,
+                                      int table_width, const int* token_row, const int* positions, const int* items, int n_items, int splits,
+                                      float* workspace, int heads, int kv_heads, int head_dim, int page_size, int pages, float scale, float softcap,
+                                      int window, int* status, cudaStream_t stream) {
+    return hb_attention_tma_tokens_biased(q, q_stride, out, out_stride, cache, block_table, table_width, token_row, positions, items, n_items, splits, workspace,
+                                          heads, kv_heads, head_dim, page_size, pages, scale, softcap, window, nullptr, 0, status, stream);
 }
 
 HB_EXPORT int hb_attention_tma_tokens(const void* q, int q_stride, void* out, int out_stride, const void* cache, const int* block_table,

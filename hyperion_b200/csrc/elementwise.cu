@@ -812,3 +812,30 @@ HB_EXPORT int hb_gelu_tanh(const void* x, void* out, int is_bf16, long long coun
     else gelu_tanh_kernel<<<blocks, 256, 0, stream>>>((const float*)x, (float*)out, (size_t)count);
     return launch_status();
 }
+
+// ---------------------------------------------------------------- a sigmoid gate on rows, in place
+// x[t, c] <- x[t, c] * scale * sigmoid(gate[t, gate_off + c]) for c < width; the gate is float, the product is rounded once.
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* __restrict__ x, int x_stride, const float* __restrict__ gate, int gate_stride, int gate_off, float scale, int width) {
+    const int t = blockIdx.y;
+    for (int c = blockIdx.x * blockDim.x + threadIdx.x; c < width; c += gridDim.x * blockDim.x) {
+        const float g = gate[(size_t)t * gate_stride + gate_off + c];
+        x[(size_t)t * x_stride + c] = from_float<T>(to_float(x[(size_t)t * x_stride + c]) * (scale / (1.f + expf(-g))));
+    }
+}
+
+HB_EXPORT int hb_sigmoid_gate(void* x, int is_bf16, int x_stride, const float* gate, int gate_stride, int gate_off, float scale, int tokens, int width,
+                              cudaStream_t stream) {
+    if (tokens <= 0 || width <= 0) return 0;
+    for (int first = 0; first < tokens; first += 65535) {
+        const int count = tokens - first < 65535 ? tokens - first : 65535;
+        const dim3 grid((width + 255) / 256 < 8 ? (width + 255) / 256 : 8, count);
+        if (is_bf16)
+            sigmoid_gate_kernel<<<grid, 256, 0, stream>>>((__nv_bfloat16*)x + (size_t)first * x_stride, x_stride, gate + (size_t)first * gate_stride, gate_stride,
+                                                          gate_off, scale, width);
+        else
+            sigmoid_gate_kernel<<<grid, 256, 0, stream>>>((float*)x + (size_t)first * x_stride, x_stride, gate + (size_t)first * gate_stride, gate_stride, gate_off,
+                                                          scale, width);
+    }
+    return launch_status();
+}

@@ -21,7 +21,7 @@ NO_POSITION_LIMIT = 1 << 30
 
 def build_spec(config: MirovikConfig) -> ModelSpec:
     width, eps = config.width, config.eps
-    layers = []
+    layers, tolerated = [], []
     for index, layer in enumerate(config.layers):
         prefix = f"l{index}."
         m = layer.mixer
@@ -43,7 +43,9 @@ def build_spec(config: MirovikConfig) -> ModelSpec:
 
         norms = {"input": norm("norm1"), "mixer_out": norm("norm1b")}
         feed_forward = None
-        if layer.mlp is not None:
+        if layer.mlp is None:  # a checkpoint may carry the feed-forward's norms all the same; nothing reads them
+            tolerated += [prefix + "norm2", prefix + "norm2b"]
+        else:
             norms.update({"post_mixer": norm("norm2"), "feed_forward_out": norm("norm2b")})
             if isinstance(layer.mlp, DenseFF):
                 feed_forward = PartSpec("activated_mlp", prefix + "mlp.", {"hidden_size": width, "intermediate_size": layer.mlp.ff, "activation": "gelu_tanh",
@@ -68,6 +70,7 @@ def build_spec(config: MirovikConfig) -> ModelSpec:
         final_norm=PartSpec("rmsnorm", "final.", {"hidden_size": width, "eps": eps, "weight_name": "norm", "one_plus": True}),
         head=PartSpec("linear_head", "", {**sizes, "tied": True}),
         offsets=offsets,
+        tolerated=tuple(tolerated),
     )
 
 

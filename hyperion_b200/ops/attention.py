@@ -39,6 +39,19 @@ def _entry(head_dim: int, page_size: int, shape: str):
     return getattr(library("attention_bf16", HB_HEAD_DIM=head_dim), f"hb_attention_{shape}_capped")
 
 
+def takes_distance_bias(head_dim: int, page_size: int) -> bool:
+    """A bias per head and distance on the scores is an argument of the TMA-fed kernels and of the tcgen05 kernel."""
+    return uses_tma(head_dim, page_size)
+
+
+def _bias_arguments(bias, heads: int, head_dim: int, page_size: int):
+    if bias.dtype != torch.float32 or bias.dim() != 2 or bias.shape[0] != heads or not bias.is_contiguous():
+        raise KernelError("attention: the distance bias is a dense float32 table [heads, span] (times log2(e))")
+    if not takes_distance_bias(head_dim, page_size):
+        raise KernelError(f"attention: no tensor-core kernel takes a distance bias with heads of {head_dim} and pages of {page_size}")
+    return ptr(bias), i32(bias.shape[1])
+
+
 def uses_tcgen05(head_dim: int, page_size: int) -> bool:
     """Head sizes 64 and 128 with pages of 8 to 64 tokens: prompt portions take the tcgen05 kernel (256-row tiles)."""
     return head_dim in (64, 128) and 8 <= page_size <= 64
@@ -96,11 +109,27 @@ def _common(q, out, cache, block_table, token_row, positions):
 
 
 def attention_tiles(q, heads, cache, block_table, token_row, positions, tiles, n_tiles, scale, window, out, tile_size: int = TILE_ROWS,
-                    softcap: float = 0.0):
+                    softcap: float = 0.0, bias=None):
     """``tile_size``: the virtual rows per tile the tiles were planned for (64, or 256 for the tcgen05 kernel).
-    ``softcap`` > 0: scores become cap * tanh(score / cap) before the softmax."""
+    ``softcap`` > 0: scores become cap * tanh(score / cap) before the softmax.  ``bias`` [heads, span] float, times log2(e):
+    the score of a key n positions back takes ``bias[head, min(n, span - 1)]``."""
     _common(q, out, cache, block_table, token_row, positions)
     pages, _, kv_heads, page_size, head_dim = cache.shape
+    if bias is not None:
+        require_cuda(bias)
+        bias_ptr, span = _bias_arguments(bias, heads, head_dim, page_size)
+        if uses_tcgen05(head_dim, page_size) and tile_size == TC_TILE_ROWS:
+            check(library("attention_tcgen05", HB_HEAD_DIM=head_dim).hb_attention_tc_tiles_biased(
+                ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table), i32(block_table.shape[1]), ptr(token_row),
+                ptr(positions), ptr(tiles), i32(n_tiles), i32(q.shape[0]), i32(heads), i32(kv_heads), i32(head_dim), i32(page_size), i32(pages),
+                f32(scale), f32(softcap or 0.0), i32(window or 0), bias_ptr, span, ptr(status_word(q.device)), ptr(work_counters(q.device)),
+                stream_ptr()), "attention_tiles")
+            return
+        check(library("attention_tma", HB_HEAD_DIM=head_dim).hb_attention_tma_tiles_biased(
+            ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table), i32(block_table.shape[1]), ptr(token_row),
+            ptr(positions), ptr(tiles), i32(n_tiles), i32(heads), i32(kv_heads), i32(head_dim), i32(page_size), i32(pages), f32(scale),
+            f32(softcap or 0.0), i32(window or 0), bias_ptr, span, ptr(status_word(q.device)), stream_ptr()), "attention_tiles")
+        return
     if uses_tcgen05(head_dim, page_size) and tile_size == TC_TILE_ROWS:
         check(library("attention_tcgen05", HB_HEAD_DIM=head_dim).hb_attention_tc_tiles_capped(
             ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table), i32(block_table.shape[1]), ptr(token_row),
@@ -115,7 +144,7 @@ def attention_tiles(q, heads, cache, block_table, token_row, positions, tiles, n
 
 
 def attention_tokens(q, heads, cache, block_table, token_row, positions, items, n_items, splits, scale, window, out, workspace=None,
-                     softcap: float = 0.0):
+                     softcap: float = 0.0, bias=None):
     _common(q, out, cache, block_table, token_row, positions)
     pages, _, kv_heads, page_size, head_dim = cache.shape
     if splits > 1:
@@ -124,10 +153,18 @@ def attention_tokens(q, heads, cache, block_table, token_row, positions, items, 
             workspace = torch.empty(need, dtype=torch.float32, device=q.device)
         elif workspace.numel() < need or workspace.dtype != torch.float32:
             raise KernelError(f"attention_tokens: workspace of {need} floats needed")
-    check(_entry(head_dim, page_size, "tokens")(ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table),
-                                  i32(block_table.shape[1]), ptr(token_row), ptr(positions), ptr(items), i32(n_items), i32(splits),
-                                  ptr(workspace), i32(heads), i32(kv_heads), i32(head_dim), i32(page_size), i32(pages), f32(scale),
-                                  f32(softcap or 0.0), i32(window or 0), ptr(status_word(q.device)), stream_ptr()), "attention_tokens")
+    if bias is not None:
+        require_cuda(bias)
+        bias_ptr, span = _bias_arguments(bias, heads, head_dim, page_size)
+        check(library("attention_tma", HB_HEAD_DIM=head_dim).hb_attention_tma_tokens_biased(
+            ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table), i32(block_table.shape[1]), ptr(token_row),
+            ptr(positions), ptr(items), i32(n_items), i32(splits), ptr(workspace), i32(heads), i32(kv_heads), i32(head_dim), i32(page_size), i32(pages),
+            f32(scale), f32(softcap or 0.0), i32(window or 0), bias_ptr, span, ptr(status_word(q.device)), stream_ptr()), "attention_tokens")
+    else:
+        check(_entry(head_dim, page_size, "tokens")(ptr(q), i32(q.stride(0)), ptr(out), i32(out.stride(0)), ptr(cache), ptr(block_table),
+                                      i32(block_table.shape[1]), ptr(token_row), ptr(positions), ptr(items), i32(n_items), i32(splits),
+                                      ptr(workspace), i32(heads), i32(kv_heads), i32(head_dim), i32(page_size), i32(pages), f32(scale),
+                                      f32(softcap or 0.0), i32(window or 0), ptr(status_word(q.device)), stream_ptr()), "attention_tokens")
     if splits > 1:
         from . import native
 

@@ -323,6 +323,15 @@ def norm_add_norm(h: torch.Tensor, y: torch.Tensor | None, w_post: torch.Tensor 
     return out
 
 
+def sigmoid_gate_(x: torch.Tensor, gate: torch.Tensor, gate_off: int, scale: float = 1.0) -> None:
+    """x[t, c] <- x[t, c] * scale * sigmoid(gate[t, gate_off + c]) in place; ``x`` may be a view of some columns, ``gate`` is float."""
+    require_cuda(x, gate)
+    if x.dim() != 2 or x.stride(1) != 1 or gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape[0] != x.shape[0]:
+        raise KernelError("sigmoid_gate: rows with unit inner stride and a float32 gate of as many rows")
+    check(library("elementwise").hb_sigmoid_gate(ptr(x), i32(is_bf16(x)), i32(x.stride(0)), ptr(gate), i32(gate.stride(0)), i32(gate_off), f32(scale),
+                                                 i32(x.shape[0]), i32(x.shape[1]), stream_ptr()), "sigmoid_gate")
+
+
 def gelu_tanh(x: torch.Tensor) -> torch.Tensor:
     """0.5 z (1 + tanh(sqrt(2 / pi) (z + 0.044715 z^3))), computed in float, in the element type of ``x``."""
     require_cuda(x)

@@ -138,14 +138,16 @@ class GroupedQueryAttention(Mixer):
             return int((rows.positions[short] + rows.counts[short]).max())
         return max(row.position + row.count for row in rows if row.count <= fast_attention.TOKEN_SHAPE_MAX)
 
-    def _attend_fast(self, qkv, step, cache):
-        out = torch.empty((step.n_tokens, self.heads * self.head_dim), dtype=self.dtype, device=qkv.device)
+    def _attend_fast(self, qkv, step, cache, out=None, bias=None):
+        """``out``: a [tokens, >= heads * head_dim] view to write to; ``bias``: a table by distance (``ops.attention.attention_tiles``)."""
+        if out is None:
+            out = torch.empty((step.n_tokens, self.heads * self.head_dim), dtype=self.dtype, device=qkv.device)
         size = fast_attention.tile_rows(self.head_dim, step.host.get("page_size"))
         key = f"attn_tiles_{fast_attention.tile_tokens(self.heads, self.kv_heads, size)}"
         n_tiles, n_items = step.host.get(key, 0), step.host.get("attn_items", 0)
         if n_tiles:
             fast_attention.attention_tiles(qkv, self.heads, cache.kv, cache.block_table, step.token_row, step.positions,
-                                           step.extra[key], n_tiles, self.scale, self.window, out, tile_size=size, softcap=self.softcap)
+                                           step.extra[key], n_tiles, self.scale, self.window, out, tile_size=size, softcap=self.softcap, bias=bias)
         if n_items:
             # a step replayed from a CUDA graph fixes its launch shape for every context its tables can hold
             longest = step.host.get("context_cap") or self._longest_short_row(step.rows)
@@ -153,7 +155,7 @@ class GroupedQueryAttention(Mixer):
                 longest = min(longest, self.window + fast_attention.KEY_TILE)
             splits = fast_attention.choose_splits(n_items, self.heads, self.kv_heads, longest)
             fast_attention.attention_tokens(qkv, self.heads, cache.kv, cache.block_table, step.token_row, step.positions,
-                                            step.extra["attn_items"], n_items, splits, self.scale, self.window, out, softcap=self.softcap)
+                                            step.extra["attn_items"], n_items, splits, self.scale, self.window, out, softcap=self.softcap, bias=bias)
         return out
 
 

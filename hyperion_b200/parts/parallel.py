@@ -37,7 +37,9 @@ from typing import Mapping
 import torch
 
 from .. import ops
+from ..ops import attention as fast_attention
 from ..ops import recurrent
+from .attention import GroupedQueryAttention
 from .base import MIXERS, POSITIONS, BuildContext, Mixer, PagedTokens, RequestState, WeightSpec, make, register_mixer
 from .spec import PartSpec
 
@@ -108,6 +110,10 @@ class BiasedAttention(Branch):
         self.q_width, self.k_width = self.heads * self.head_dim, self.kv_heads * self.head_dim
         self.v_width, self.core_width = self.kv_heads * self.value_dim, self.heads * self.value_dim
         self.in_width = self.q_width + self.k_width + self.v_width + self.core_width
+        # keys and values of one size that the TMA-fed kernels take, in bfloat16: the tensor-core kernels of the package's other
+        # attentions read the pages (tcgen05 tiles for prompt portions, split keys for decoded tokens), with the bias as an argument
+        self.window, self.softcap = 0, 0.0
+        self.fast = self.dtype == torch.bfloat16 and self.value_dim == self.head_dim and self.head_dim % 64 == 0
 
     def weights(self) -> dict[str, WeightSpec]:
         h = self.hidden
@@ -125,6 +131,7 @@ class BiasedAttention(Branch):
             raise ValueError(f"a distance bias of {buckets} buckets needs bias_max above {buckets // 2}, got {self.bias_max}")
         index = torch.tensor([distance_bucket(n, buckets, self.bias_max) for n in range(self.bias_max + 1)], dtype=torch.long, device=rel.device)
         self.by_distance = rel[index].t().contiguous()  # [heads, bias_max + 1]
+        self.by_distance_log2 = (self.by_distance * math.log2(math.e)).contiguous() if self.fast else None  # the fast kernels' softmax is in base 2
 
     def cache_request(self):
         if self.value_dim == self.head_dim:
@@ -132,7 +139,17 @@ class BiasedAttention(Branch):
         return PagedTokens((self.kv_heads,), (self.head_dim + self.value_dim,), 0)
 
     def kernel_modules(self):
-        return [("heads_prepare", {}), ("attention_generic", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
+        modules = [("heads_prepare", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
+        if not self.fast:
+            return modules + [("attention_generic", {})]
+        modules += [("elementwise", {}), ("attention_tma", {"HB_HEAD_DIM": self.head_dim})]  # which is launched depends on the page size of the cache
+        if self.head_dim in (64, 128):
+            modules.append(("attention_tcgen05", {"HB_HEAD_DIM": self.head_dim}))
+        return modules
+
+    step_plans = GroupedQueryAttention.step_plans  # the rows of a step cut into tiles and single tokens, as for every attention of the package
+    _attend_fast = GroupedQueryAttention._attend_fast
+    _longest_short_row = staticmethod(GroupedQueryAttention._longest_short_row)
 
     def core(self, proj, col0, step, cache, out, scale):
         q = torch.empty((proj.shape[0], self.q_width), dtype=self.dtype, device=proj.device)
@@ -141,6 +158,10 @@ class BiasedAttention(Branch):
         ops.heads_prepare_wide(proj, col0, k_off, v_off, self.heads, self.kv_heads, self.head_dim, self.value_dim, step.positions, q_out=q,
                                q_norm=self.q_norm, k_norm=self.k_norm, norm_whole=True, eps=self.eps, cache=cache.kv, block_table=cache.block_table,
                                token_row=step.token_row, page_size=cache.page_size)
+        if self.fast and fast_attention.takes_distance_bias(self.head_dim, cache.page_size):
+            self._attend_fast(q, step, cache, out=out, bias=self.by_distance_log2)
+            ops.sigmoid_gate_(out, proj, v_off + self.v_width, scale)
+            return
         ops.attention_general(q, self.heads, self.kv_heads, self.head_dim, self.value_dim, cache.kv, cache.block_table, step.token_row, step.positions,
                               cache.page_size, self.scale, distance_bias=self.by_distance, gate=proj, gate_off=v_off + self.v_width, out_scale=scale, out=out)
 
