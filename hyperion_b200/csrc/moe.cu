@@ -7,7 +7,7 @@
 //   route:    z = W_r x in float (one sequential chain of fixed shape per logit), the `top` largest logits by selection
 //             (lowest index first among equals), weight = sigmoid(z) of the chosen (not renormalised) or 1
 //   plan:     per expert a run of slots, padded to a multiple of `pad`; slot_of[token, choice]; per slot its token (or -1)
-//             and its weight; per tile of `pad` slots its expert (or -1)
+//             and its weight; per tile of `pad` slots its expert (or -1) and how many of its slots are taken
 //   gather:   xs[slot] = weight * x[token] (the weight multiplies what the expert reads); padding rows are left as they are
 //   product:  C[slot] = A[slot] W[expert of slot's tile]^T, float accumulation in one chain over k per output
 //   combine:  out[token] = base[token] + sum over choices of y[slot_of[token, choice]], in the order of the choices
@@ -54,12 +54,12 @@ constexpr int PLAN_THREADS = 1024;
 __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const int* __restrict__ chosen, const float* __restrict__ weights, int pairs, int top,
                                                                 int experts, int pad, int capacity, int* __restrict__ slot_of,
                                                                 int* __restrict__ slot_token, float* __restrict__ slot_weight,
-                                                                int* __restrict__ tile_expert) {
+                                                                int* __restrict__ tile_expert, int* __restrict__ tile_rows) {
     __shared__ int count[1024], start[1024];
     const int tid = threadIdx.x;
     for (int e = tid; e < experts; e += PLAN_THREADS) count[e] = 0;
     for (int s = tid; s < capacity; s += PLAN_THREADS) { slot_token[s] = -1; slot_weight[s] = 0.f; }
-    for (int i = tid; i < capacity / pad; i += PLAN_THREADS) tile_expert[i] = -1;
+    for (int i = tid; i < capacity / pad; i += PLAN_THREADS) { tile_expert[i] = -1; tile_rows[i] = 0; }
     __syncthreads();
     for (int i = tid; i < pairs; i += PLAN_THREADS) atomicAdd(&count[chosen[i]], 1);
     __syncthreads();
@@ -68,7 +68,10 @@ __global__ void __launch_bounds__(PLAN_THREADS) moe_plan_kernel(const int* __res
         for (int e = 0; e < experts; ++e) {
             start[e] = at;
             const int tiles = (count[e] + pad - 1) / pad;
-            for (int i = 0; i < tiles; ++i) tile_expert[at / pad + i] = e;
+            for (int i = 0; i < tiles; ++i) {
+                tile_expert[at / pad + i] = e;
+                tile_rows[at / pad + i] = min(pad, count[e] - i * pad);
+            }
             at += tiles * pad;
             count[e] = 0;  // from here on: the cursor inside the expert's run
         }
@@ -176,13 +179,14 @@ HB_EXPORT int hb_moe_route(const void* x, int is_bf16, int x_stride, const float
     return launch_status();
 }
 
-// capacity: a multiple of pad, at least pairs + experts * (pad - 1) rounded up to it.  tile_expert has capacity / pad entries.
+// capacity: a multiple of pad, at least pairs + experts * (pad - 1) rounded up to it.  tile_expert and tile_rows (the real rows at the start
+// of a tile) have capacity / pad entries.
 HB_EXPORT int hb_moe_plan(const int* chosen, const float* weights, int pairs, int top, int experts, int pad, int capacity, int* slot_of,
-                          int* slot_token, float* slot_weight, int* tile_expert, cudaStream_t stream) {
+                          int* slot_token, float* slot_weight, int* tile_expert, int* tile_rows, cudaStream_t stream) {
     if (pairs <= 0) return 0;
     if (experts <= 0 || experts > 1024 || pad <= 0 || capacity % pad || top <= 0) return HB_UNSUPPORTED_SIZE;
     if ((long long)capacity < (long long)pairs + (long long)experts * (pad - 1)) return HB_BAD_ARGUMENT;
-    moe_plan_kernel<<<1, PLAN_THREADS, 0, stream>>>(chosen, weights, pairs, top, experts, pad, capacity, slot_of, slot_token, slot_weight, tile_expert);
+    moe_plan_kernel<<<1, PLAN_THREADS, 0, stream>>>(chosen, weights, pairs, top, experts, pad, capacity, slot_of, slot_token, slot_weight, tile_expert, tile_rows);
     return launch_status();
 }
 

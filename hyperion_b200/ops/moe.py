@@ -8,9 +8,11 @@ from dataclasses import dataclass
 
 import torch
 
+from .basic import status_word
 from .native import KernelError, check, i32, is_bf16, library, ptr, require_cuda, stream_ptr
 
 PAD = 128  # an expert's rows are padded to whole tiles of this many rows
+FEW_PAIRS = 128  # steps of at most this many (token, choice) pairs stream the matrices of the experts they use instead of taking tensor-core tiles
 
 
 @dataclass
@@ -23,6 +25,8 @@ class Plan:
     slot_token: torch.Tensor  # [capacity] int32: the token of a row, -1 for padding
     slot_weight: torch.Tensor  # [capacity] float: what the row's input is multiplied by
     tile_expert: torch.Tensor  # [capacity / PAD] int32: the expert of a tile of rows, -1 beyond the last used tile
+    tile_rows: torch.Tensor  # [capacity / PAD] int32: how many rows of a tile are taken (they come first)
+    pairs: int = 0
 
 
 def route(x: torch.Tensor, router: torch.Tensor, top: int, weighted: bool = True) -> tuple[torch.Tensor, torch.Tensor]:
@@ -52,9 +56,10 @@ def plan(chosen: torch.Tensor, weights: torch.Tensor, experts: int) -> Plan:
     capacity = capacity_for(pairs, experts)
     device = chosen.device
     out = Plan(capacity, top, torch.empty(pairs, dtype=torch.int32, device=device), torch.empty(capacity, dtype=torch.int32, device=device),
-               torch.empty(capacity, dtype=torch.float32, device=device), torch.empty(capacity // PAD, dtype=torch.int32, device=device))
+               torch.empty(capacity, dtype=torch.float32, device=device), torch.empty(capacity // PAD, dtype=torch.int32, device=device),
+               torch.empty(capacity // PAD, dtype=torch.int32, device=device), pairs)
     check(library("moe").hb_moe_plan(ptr(chosen), ptr(weights), i32(pairs), i32(top), i32(experts), i32(PAD), i32(capacity), ptr(out.slot_of),
-                                     ptr(out.slot_token), ptr(out.slot_weight), ptr(out.tile_expert), stream_ptr()), "moe_plan")
+                                     ptr(out.slot_token), ptr(out.slot_weight), ptr(out.tile_expert), ptr(out.tile_rows), stream_ptr()), "moe_plan")
     return out
 
 
@@ -70,12 +75,27 @@ def gather(x: torch.Tensor, where: Plan) -> torch.Tensor:
     return out
 
 
+def takes_tensor_cores(a: torch.Tensor, w: torch.Tensor) -> bool:
+    """bfloat16 operands whose rows are multiples of 16 bytes go to ``csrc/moe_gemm_tcgen05.cu``; everything else (float32, where
+    every output is one chain of fused multiply-adds whatever the step's size, and odd sizes) to the plain kernel."""
+    return a.dtype == torch.bfloat16 and a.shape[1] % 8 == 0 and a.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+
+
 def grouped_linear(a: torch.Tensor, w: torch.Tensor, where: Plan) -> torch.Tensor:
     """``a`` [capacity, k] times the matrix of each tile's expert: ``w`` [experts, n, k] -> [capacity, n], float accumulation."""
     require_cuda(a, w)
     if a.dtype != w.dtype or not a.is_contiguous() or not w.is_contiguous() or w.dim() != 3 or w.shape[2] != a.shape[1] or a.shape[0] != where.capacity:
         raise KernelError("moe.grouped_linear: dense operands of one element type, rows [capacity, k] and matrices [experts, n, k]")
     out = torch.empty((where.capacity, w.shape[1]), dtype=a.dtype, device=a.device)
+    if takes_tensor_cores(a, w):
+        lib = library("moe_gemm_tcgen05")
+        if where.pairs <= FEW_PAIRS:
+            check(lib.hb_moe_gemm_rows(ptr(a), ptr(w), ptr(out), ptr(where.tile_expert), ptr(where.tile_rows), i32(PAD), i32(where.capacity), i32(w.shape[1]),
+                                       i32(w.shape[2]), stream_ptr()), "moe_gemm_rows")
+        else:
+            check(lib.hb_moe_gemm_tiles(ptr(a), ptr(w), ptr(out), ptr(where.tile_expert), i32(where.capacity), i32(w.shape[0]), i32(w.shape[1]),
+                                        i32(w.shape[2]), ptr(status_word(a.device)), stream_ptr()), "moe_gemm_tiles")
+        return out
     check(library("moe").hb_moe_gemm(ptr(a), ptr(w), ptr(out), i32(is_bf16(a)), ptr(where.tile_expert), i32(PAD), i32(where.capacity), i32(w.shape[1]),
                                      i32(w.shape[2]), stream_ptr()), "moe_gemm")
     return out

@@ -57,6 +57,8 @@ class RoutedExperts(FeedForward):
 
     def kernel_modules(self):
         modules = [("moe", {}), ("elementwise", {})]
+        if self.dtype == torch.bfloat16 and self.hidden % 8 == 0 and self.inter % 8 == 0:
+            modules.append(("moe_gemm_tcgen05", {}))
         return modules + (self.shared.kernel_modules() if self.shared is not None else [])
 
     def forward(self, x, step):

@@ -331,12 +331,15 @@ def test_norm_of_the_output_then_add_then_norm_of_the_sum(out_dtype):
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_routing_sorting_and_summing_of_experts(dtype):
     """The router's choices and weights, every pair in a slot of its expert's run, the grouped product against one product per
-    expert, and the sum of a token's rows, with more experts than tokens and with experts that no token chose."""
+    expert, and the sum of a token's rows, with more experts than tokens and with experts that no token chose.  In bfloat16 the
+    sizes take all three kernels of the product: tensor-core tiles (many pairs, rows of whole 16 bytes), the streaming kernel
+    (few pairs) and the plain one (other sizes)."""
     from hyperion_b200.ops import moe
 
     dev = torch.device("cuda", 0)
     g = torch.Generator().manual_seed(8)
-    for tokens, hidden, count, top, inner in ((37, 48, 5, 2, 20), (3, 24, 9, 3, 7), (300, 64, 4, 1, 130), (1, 16, 2, 2, 5)):
+    for tokens, hidden, count, top, inner in ((37, 48, 5, 2, 20), (3, 24, 9, 3, 7), (300, 64, 4, 1, 130), (1, 16, 2, 2, 5), (300, 72, 4, 1, 136),
+                                              (200, 128, 3, 2, 256), (5, 64, 8, 2, 40)):
         x = torch.randn(tokens, hidden, generator=g).to(dtype)
         router = torch.randn(count, hidden, generator=g)
         router[count - 1] = -5 * x.float().mean(dim=0) if tokens > 1 else router[count - 1]  # an expert that is rarely chosen
@@ -353,7 +356,9 @@ def test_routing_sorting_and_summing_of_experts(dtype):
             for k in range(top):
                 slot = int(slot_of[t, k])
                 assert slot_token[slot] == t and tile_expert[slot // moe.PAD] == chosen[t, k]
-        assert int((slot_token >= 0).sum()) == tokens * top
+        assert int((slot_token >= 0).sum()) == tokens * top == int(where.tile_rows.sum())
+        assert all(int(r) == int((slot_token[i * moe.PAD:(i + 1) * moe.PAD] >= 0).sum()) and bool((slot_token[i * moe.PAD:i * moe.PAD + int(r)] >= 0).all())
+                   for i, r in enumerate(where.tile_rows.cpu()))  # the taken slots of a tile come first
         rows = moe.gather(x.to(dev), where)
         w = (torch.randn(count, inner, hidden, generator=g) / hidden ** 0.5).to(dtype)
         y = moe.grouped_linear(rows, w.to(dev), where)
