@@ -14,23 +14,40 @@
 #include "common.cuh"
 
 namespace {
-constexpr int ROUTE_THREADS = 128;
+constexpr int ROUTE_THREADS = 256;
 
+// One block per token: the row in shared memory as floats, a warp per expert at a time.  A lane adds up every 32nd group of four
+// columns in four chains of its own (columns beyond a multiple of four go to the first chain), the chains are added in a fixed
+// order and the lanes meet in a butterfly: a logit depends on nothing but the row and the expert's weights.
 template <typename T>
 __global__ void __launch_bounds__(ROUTE_THREADS) moe_route_kernel(const T* __restrict__ x, int x_stride, const float* __restrict__ router, int hidden,
                                                                   int experts, int top, int weighted, int* __restrict__ chosen,
                                                                   float* __restrict__ weights) {
-    extern __shared__ float shared[];  // the token's row, then one logit per expert
+    extern __shared__ __align__(16) float shared[];  // the token's row (padded to a multiple of four), then one logit per expert
     float* row = shared;
-    float* logit = shared + hidden;
+    const int padded = (hidden + 3) & ~3;
+    float* logit = shared + padded;
     const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    for (int i = threadIdx.x; i < hidden; i += ROUTE_THREADS) row[i] = to_float(x[(size_t)t * x_stride + i]);
+    for (int i = threadIdx.x; i < padded; i += ROUTE_THREADS) row[i] = i < hidden ? to_float(x[(size_t)t * x_stride + i]) : 0.f;
     __syncthreads();
+    const bool by_four = (hidden & 3) == 0 && (((uintptr_t)router) & 15) == 0;
     for (int e = warp; e < experts; e += ROUTE_THREADS / 32) {
         const float* w = router + (size_t)e * hidden;
-        float sum = 0.f;
-        for (int i = lane; i < hidden; i += 32) sum = fmaf(row[i], w[i], sum);
-        sum = warp_sum(sum);
+        float part[4] = {0.f, 0.f, 0.f, 0.f};
+        if (by_four) {
+#pragma unroll 4
+            for (int i = lane * 4; i < hidden; i += 128) {
+                const float4 wv = *reinterpret_cast<const float4*>(w + i), rv = *reinterpret_cast<const float4*>(row + i);
+                part[0] = fmaf(rv.x, wv.x, part[0]); part[1] = fmaf(rv.y, wv.y, part[1]);
+                part[2] = fmaf(rv.z, wv.z, part[2]); part[3] = fmaf(rv.w, wv.w, part[3]);
+            }
+        } else {
+            for (int i = lane * 4; i < hidden; i += 128)
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (i + j < hidden) part[j] = fmaf(row[i + j], w[i + j], part[j]);
+        }
+        const float sum = warp_sum((part[0] + part[1]) + (part[2] + part[3]));
         if (lane == 0) logit[e] = sum;
     }
     __syncthreads();
@@ -151,6 +168,51 @@ __global__ void __launch_bounds__(256) moe_gemm_kernel(const T* __restrict__ a, 
     }
 }
 
+// The two above for bfloat16 rows that are whole 16-byte pieces: eight values per thread and access.
+__global__ void moe_gather_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, int x_stride, const int* __restrict__ slot_token,
+                                         const float* __restrict__ slot_weight, __nv_bfloat16* __restrict__ out, int hidden) {
+    const int slot = blockIdx.x, t = slot_token[slot];
+    if (t < 0) return;
+    const float w = slot_weight[slot];
+    for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + (size_t)t * x_stride + i);
+        const __nv_bfloat162* in = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        uint4 packed;
+        __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(in[j]);
+            o[j] = __floats2bfloat162_rn(f.x * w, f.y * w);
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)slot * hidden + i) = packed;
+    }
+}
+
+__global__ void moe_combine_bf16x8_kernel(const __nv_bfloat16* __restrict__ y, const int* __restrict__ slot_of, int top,
+                                          const __nv_bfloat16* __restrict__ base, __nv_bfloat16* __restrict__ out, int hidden) {
+    const int t = blockIdx.x;
+    for (int i = threadIdx.x * 8; i < hidden; i += blockDim.x * 8) {
+        float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        if (base) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(base + (size_t)t * hidden + i);
+            const __nv_bfloat162* in = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(in[j]); sum[2 * j] = f.x; sum[2 * j + 1] = f.y; }
+        }
+        for (int k = 0; k < top; ++k) {
+            const uint4 raw = *reinterpret_cast<const uint4*>(y + (size_t)slot_of[(size_t)t * top + k] * hidden + i);
+            const __nv_bfloat162* in = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { const float2 f = __bfloat1622float2(in[j]); sum[2 * j] += f.x; sum[2 * j + 1] += f.y; }
+        }
+        uint4 packed;
+        __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) o[j] = __floats2bfloat162_rn(sum[2 * j], sum[2 * j + 1]);
+        *reinterpret_cast<uint4*>(out + (size_t)t * hidden + i) = packed;
+    }
+}
+
 template <typename TY, typename TB, typename TO>
 __global__ void moe_combine_kernel(const TY* __restrict__ y, const int* __restrict__ slot_of, int top, const TB* __restrict__ base, TO* __restrict__ out,
                                    int hidden) {
@@ -167,7 +229,7 @@ HB_EXPORT int hb_moe_route(const void* x, int is_bf16, int x_stride, const float
                            int* chosen, float* weights, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (experts <= 0 || experts > 1024 || top <= 0 || top > experts || hidden <= 0) return HB_UNSUPPORTED_SIZE;
-    const size_t shared = (size_t)(hidden + experts) * sizeof(float);
+    const size_t shared = (size_t)(((hidden + 3) & ~3) + experts) * sizeof(float);
     if (shared > 200 * 1024) return HB_UNSUPPORTED_SIZE;
     if (is_bf16) {
         if (shared > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)shared);
@@ -194,6 +256,11 @@ HB_EXPORT int hb_moe_gather(const void* x, int is_bf16, int x_stride, const int*
                             int hidden, cudaStream_t stream) {
     if (capacity <= 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
+    if (is_bf16 && hidden % 8 == 0 && x_stride % 8 == 0 && (((uintptr_t)x | (uintptr_t)out) & 15) == 0) {
+        moe_gather_bf16x8_kernel<<<capacity, hidden >= 2048 ? 256 : 128, 0, stream>>>((const __nv_bfloat16*)x, x_stride, slot_token, slot_weight,
+                                                                                     (__nv_bfloat16*)out, hidden);
+        return launch_status();
+    }
     if (is_bf16) moe_gather_kernel<<<capacity, threads, 0, stream>>>((const __nv_bfloat16*)x, x_stride, slot_token, slot_weight, (__nv_bfloat16*)out, hidden);
     else moe_gather_kernel<<<capacity, threads, 0, stream>>>((const float*)x, x_stride, slot_token, slot_weight, (float*)out, hidden);
     return launch_status();
@@ -216,6 +283,11 @@ HB_EXPORT int hb_moe_combine(const void* y, const int* slot_of, int top, const v
                              cudaStream_t stream) {
     if (tokens <= 0) return 0;
     const int threads = hidden >= 1024 ? 256 : 128;
+    if (is_bf16 && hidden % 8 == 0 && (((uintptr_t)y | (uintptr_t)base | (uintptr_t)out) & 15) == 0) {
+        moe_combine_bf16x8_kernel<<<tokens, hidden >= 2048 ? 256 : 128, 0, stream>>>((const __nv_bfloat16*)y, slot_of, top, (const __nv_bfloat16*)base,
+                                                                                    (__nv_bfloat16*)out, hidden);
+        return launch_status();
+    }
     if (is_bf16)
         moe_combine_kernel<<<tokens, threads, 0, stream>>>((const __nv_bfloat16*)y, slot_of, top, (const __nv_bfloat16*)base, (__nv_bfloat16*)out, hidden);
     else
