@@ -177,6 +177,91 @@ __global__ void __launch_bounds__(THREADS) heads_prepare_wide_kernel(
 }
 }  // namespace
 
+// The same work with one block per token, for the cases in which a token's heads have something in common: a norm over the whole
+// projection (its sum of squares is taken once, not once per head) and the rotation (a token's sines and cosines are taken once
+// and serve every head).  Per-head norms stay with the kernel above.
+namespace {
+constexpr int TOKEN_THREADS = 256, MAX_PAIRS = 128;
+
+template <typename TO, typename Place>
+__device__ __forceinline__ void prepare_heads_of_token(const float* all, int heads, int head_dim, const float* w, float inv, float post, int pairs,
+                                                       int rot_half, const float* cs, const float* sn, Place place) {
+    for (int item = threadIdx.x; item < heads * pairs; item += TOKEN_THREADS) {
+        const int head = item / pairs, i = item - head * pairs;
+        const int a = rot_half ? i : 2 * i, b = rot_half ? i + pairs : 2 * i + 1;
+        const float* p = all + (size_t)head * head_dim;
+        const float* wh = w ? w + (size_t)head * head_dim : nullptr;
+        const float u = p[a] * inv * (wh ? wh[a] : 1.f), v = p[b] * inv * (wh ? wh[b] : 1.f);
+        TO* dst = place(head);
+        if (!dst) continue;
+        dst[a] = from_float<TO>((u * cs[i] - v * sn[i]) * post);
+        dst[b] = from_float<TO>((v * cs[i] + u * sn[i]) * post);
+    }
+    const int rest = head_dim - 2 * pairs;
+    for (int item = threadIdx.x; item < heads * rest; item += TOKEN_THREADS) {
+        const int head = item / rest, d = 2 * pairs + (item - head * rest);
+        TO* dst = place(head);
+        if (!dst) continue;
+        dst[d] = from_float<TO>(all[(size_t)head * head_dim + d] * inv * (w ? w[(size_t)head * head_dim + d] : 1.f) * post);
+    }
+}
+
+template <typename TO>
+__global__ void __launch_bounds__(TOKEN_THREADS) heads_prepare_token_kernel(
+    const float* x, int stride, int q_off, int k_off, int v_off, int q_heads, int kv_heads, int head_dim, int v_dim,
+    const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps, const float* __restrict__ inv_freq, int rot_dims, int rot_half,
+    const int* __restrict__ positions, float k_scale, TO* q_out, int q_out_stride, TO* k_out, int k_out_stride, TO* __restrict__ k_cache,
+    TO* __restrict__ v_cache, size_t page_stride, size_t head_stride, int token_stride, const int* __restrict__ block_table, int table_width,
+    const int* __restrict__ token_row, int page_size, int pages, int* status) {
+    __shared__ float scratch[32];
+    __shared__ float cs[MAX_PAIRS], sn[MAX_PAIRS];
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const float* row = x + (size_t)t * stride;
+    const int pairs = inv_freq ? rot_dims / 2 : 0;
+    for (int i = threadIdx.x; i < pairs; i += TOKEN_THREADS) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
+    float inv_q = 1.f, inv_k = 1.f;
+    if (q_norm) {
+        float sum = 0.f;
+        for (int i = threadIdx.x; i < q_heads * head_dim; i += TOKEN_THREADS) sum = fmaf(row[q_off + i], row[q_off + i], sum);
+        inv_q = 1.0f / sqrtf(block_sum(sum, scratch) / (float)(q_heads * head_dim) + eps);
+    }
+    if (k_norm) {
+        float sum = 0.f;
+        for (int i = threadIdx.x; i < kv_heads * head_dim; i += TOKEN_THREADS) sum = fmaf(row[k_off + i], row[k_off + i], sum);
+        inv_k = 1.0f / sqrtf(block_sum(sum, scratch) / (float)(kv_heads * head_dim) + eps);
+    }
+    __syncthreads();  // the sines and cosines are there
+    int page = -1, slot = 0;
+    if (k_cache) {
+        const int block = pos / page_size;
+        page = (pos >= 0 && block < table_width) ? block_table[(size_t)token_row[t] * table_width + block] : -1;
+        if (page < 0 || page >= pages) {
+            if (threadIdx.x == 0) atomicOr(status, HB_STATUS_BAD_PAGE);
+            page = -1;
+        }
+        slot = pos - block * page_size;
+    }
+    prepare_heads_of_token<TO>(row + q_off, q_heads, head_dim, q_norm, inv_q, 1.f, pairs, rot_half, cs, sn,
+                               [&](int head) { return q_out + (size_t)t * q_out_stride + (size_t)head * head_dim; });
+    if (k_cache) {
+        TO* key_page = page >= 0 ? k_cache + (size_t)page * page_stride + (size_t)slot * token_stride : nullptr;
+        prepare_heads_of_token<TO>(row + k_off, kv_heads, head_dim, k_norm, inv_k, k_scale, pairs, rot_half, cs, sn,
+                                   [&](int head) { return key_page ? key_page + (size_t)head * head_stride : nullptr; });
+        if (page >= 0) {
+            TO* value_page = v_cache + (size_t)page * page_stride + (size_t)slot * token_stride;
+            for (int item = threadIdx.x; item < kv_heads * v_dim; item += TOKEN_THREADS) {
+                const int head = item / v_dim, d = item - head * v_dim;
+                value_page[(size_t)head * head_stride + d] = from_float<TO>(row[v_off + item]);
+            }
+        }
+    } else {
+        prepare_heads_of_token<TO>(row + k_off, kv_heads, head_dim, k_norm, inv_k, k_scale, pairs, rot_half, cs, sn,
+                                   [&](int head) { return k_out + (size_t)t * k_out_stride + (size_t)head * head_dim; });
+    }
+}
+}  // namespace
+
 // x [tokens, stride] float with queries at q_off, keys at k_off, values at v_off.  q_out is always given; keys go to the cache
 // (k_cache and v_cache given, values too) or to k_out (values then stay where they are).
 HB_EXPORT int hb_heads_prepare_wide(const float* x, int tokens, int stride, int q_off, int k_off, int v_off, int q_heads, int kv_heads, int head_dim,
@@ -189,6 +274,21 @@ HB_EXPORT int hb_heads_prepare_wide(const float* x, int tokens, int stride, int 
     if (head_dim <= 0 || v_dim <= 0 || rot_dims < 0 || rot_dims > head_dim || (rot_dims & 1) || !q_out || (!k_cache && !k_out)) return HB_UNSUPPORTED_SIZE;
     const int heads = q_heads + kv_heads + (k_cache ? kv_heads : 0);
     if (heads <= 0 || heads > 65535) return HB_UNSUPPORTED_SIZE;
+    if ((norm_whole || (!q_norm && !k_norm)) && rot_dims / 2 <= MAX_PAIRS) {  // one block per token
+        if (out_is_bf16)
+            heads_prepare_token_kernel<<<tokens, TOKEN_THREADS, 0, stream>>>(x, stride, q_off, k_off, v_off, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, eps,
+                                                                             inv_freq, rot_dims, rot_half, positions, k_scale, (__nv_bfloat16*)q_out, q_out_stride,
+                                                                             (__nv_bfloat16*)k_out, k_out_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
+                                                                             (size_t)page_stride, (size_t)head_stride, token_stride, block_table, table_width,
+                                                                             token_row, page_size, pages, status);
+        else
+            heads_prepare_token_kernel<<<tokens, TOKEN_THREADS, 0, stream>>>(x, stride, q_off, k_off, v_off, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, eps,
+                                                                             inv_freq, rot_dims, rot_half, positions, k_scale, (float*)q_out, q_out_stride,
+                                                                             (float*)k_out, k_out_stride, (float*)k_cache, (float*)v_cache, (size_t)page_stride,
+                                                                             (size_t)head_stride, token_stride, block_table, table_width, token_row, page_size,
+                                                                             pages, status);
+        return launch_status();
+    }
     const dim3 grid(tokens, heads);
     if (out_is_bf16)
         heads_prepare_wide_kernel<<<grid, THREADS, 0, stream>>>(x, stride, q_off, k_off, v_off, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, norm_whole,

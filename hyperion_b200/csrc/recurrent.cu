@@ -75,7 +75,7 @@ struct ScanArgs {
     int state_off;
     const int* slots;
     const int* row_start;
-    float* out;          // [tokens, heads * e]
+    float* out;          // [tokens, heads * e], or null: only the states are wanted
     int heads, groups, n, n_padded, e;
     float q_scale;
 };
@@ -246,7 +246,7 @@ __global__ void __launch_bounds__(SCAN_THREADS) state_scan_kernel(const ScanArgs
             for (int c = 0; c < CPT; ++c) {
                 const int col = col0 + cw + GROUPS * c;
                 const float out = MODE == MODE_STATE_SPACE ? fmaf(skip, cv[c], o[c]) : o[c];
-                if (l == 0 && col < a.e) a.out[((size_t)(first + j) * a.heads + head) * a.e + col] = out;
+                if (l == 0 && col < a.e && a.out) a.out[((size_t)(first + j) * a.heads + head) * a.e + col] = out;
             }
         }
         if (!more) break;
@@ -570,4 +570,49 @@ HB_EXPORT int hb_selective_scan(const float* x, int x_stride, const float* dt, i
     const SelectiveArgs args{x, x_stride, dt, dt_stride, bc, bc_stride, b_off, c_off, a, skip, gate, gate_stride, gate_off, state, (size_t)slot_stride,
                              state_off, slots, row_start, out, out_stride, inner, n, n_padded};
     return out_is_bf16 ? launch_selective<__nv_bfloat16>(args, rows, stream) : launch_selective<float>(args, rows, stream);
+}
+
+
+// ---------------------------------------------------------------- joining the segments of a row that were scanned side by side
+// A recurrence that is linear in its state, S <- a S + (something that does not depend on S), can be walked in segments that do not
+// wait for one another: every segment is first scanned from a zero state, which gives what it adds (its end state E_j); with the
+// segment's total decay A_j the state at the start of segment j + 1 is S_{j+1} = A_j S_j + E_j, a short loop per state entry; then
+// every segment is scanned again from its true start.  This kernel is the loop, for a constant decay per head (A_j = decay^length):
+// ends[j] holds E_j on entry and S_j on return, and the row's state record ends up holding the state after its last segment.
+// The result differs from the one-pass scan by rounding only; it is used where bits need not repeat across cuts of the work.
+namespace {
+__global__ void join_segments_kernel(float* __restrict__ ends, size_t end_stride, float* __restrict__ state, size_t slot_stride, int state_off,
+                                     const int* __restrict__ slots, const int* __restrict__ seg_start, const int* __restrict__ seg_row, int segments,
+                                     const float* __restrict__ decay, int per_head, int entries) {
+    const int entry = blockIdx.x * blockDim.x + threadIdx.x;
+    if (entry >= entries) return;
+    const float log_decay = log2f(decay[entry / per_head]);
+    int j = 0;
+    while (j < segments) {
+        const int row = seg_row[j];
+        float* kept = state + (size_t)slots[row] * slot_stride + state_off + entry;
+        float s = *kept;
+        for (; j < segments && seg_row[j] == row; ++j) {
+            const float added = ends[(size_t)j * end_stride + entry];
+            ends[(size_t)j * end_stride + entry] = s;
+            const int length = seg_start[j + 1] - seg_start[j];
+            const float fade = log_decay == 0.f ? 1.f : exp2f((float)length * log_decay);
+            s = fmaf(fade, s, added);
+        }
+        *kept = s;
+    }
+}
+}  // namespace
+
+// ends [segments, end_stride] float: entry e of segment j at ends[j * end_stride + e], e < entries = heads * per_head; the state of
+// row r at state + slots[r] * slot_stride + state_off.  Segments of one row follow one another; seg_start has segments + 1 entries.
+HB_EXPORT int hb_join_segments(float* ends, long long end_stride, float* state, long long slot_stride, int state_off, const int* slots,
+                               const int* seg_start, const int* seg_row, int segments, const float* decay, int heads, int per_head,
+                               cudaStream_t stream) {
+    if (segments <= 0) return 0;
+    if (heads <= 0 || per_head <= 0) return HB_BAD_ARGUMENT;
+    const int entries = heads * per_head;
+    join_segments_kernel<<<(entries + 255) / 256, 256, 0, stream>>>(ends, (size_t)end_stride, state, (size_t)slot_stride, state_off, slots, seg_start, seg_row,
+                                                                 segments, decay, per_head, entries);
+    return launch_status();
 }

@@ -45,11 +45,13 @@ def conv_state_update(x: torch.Tensor, col0: int, channels: int, taps: int, stat
 
 def state_scan(mode: int, conv: torch.Tensor, k_off: int, q_off: int, v_off: int, proj: torch.Tensor, decay_off: int, step_off: int,
                a_log: torch.Tensor, dt_bias: torch.Tensor, skip: torch.Tensor | None, state: torch.Tensor, state_off: int, slots: torch.Tensor,
-               row_start: torch.Tensor, rows: int, heads: int, groups: int, n: int, n_padded: int, e: int, q_scale: float = 1.0) -> torch.Tensor:
-    """Walk every row's tokens through the recurrence of ``mode`` from and into its slot of ``state``; returns [tokens, heads * e]."""
+               row_start: torch.Tensor, rows: int, heads: int, groups: int, n: int, n_padded: int, e: int, q_scale: float = 1.0,
+               states_only: bool = False) -> torch.Tensor | None:
+    """Walk every row's tokens through the recurrence of ``mode`` from and into its slot of ``state``; returns [tokens, heads * e]
+    (nothing with ``states_only``: the walk then only leaves the rows' states)."""
     require_cuda(conv, proj, a_log, dt_bias, skip, state, slots, row_start)
     _floats(conv, proj, a_log, dt_bias, skip, state)
-    out = torch.empty((conv.shape[0], heads * e), dtype=torch.float32, device=conv.device)
+    out = None if states_only else torch.empty((conv.shape[0], heads * e), dtype=torch.float32, device=conv.device)
     check(library("recurrent").hb_state_scan(i32(mode), ptr(conv), i32(conv.stride(0)), i32(k_off), i32(q_off), i32(v_off), ptr(proj), i32(proj.stride(0)),
                                              i32(decay_off), i32(step_off), ptr(a_log), ptr(dt_bias), ptr(skip), ptr(state),
                                              ctypes.c_longlong(state.stride(0)), i32(state_off), ptr(slots), ptr(row_start), ptr(out), i32(rows),
@@ -96,3 +98,38 @@ def selective_scan(x: torch.Tensor, dt: torch.Tensor, bc: torch.Tensor, b_off: i
                                                  i32(state_off), ptr(slots), ptr(row_start), ptr(out), i32(is_bf16(out)), i32(out.stride(0)), i32(rows),
                                                  i32(inner), i32(n), i32(n_padded), stream_ptr()), "selective_scan")
     return out
+
+
+SEGMENT = 256  # tokens per segment when a long row's scan is cut into segments that run side by side
+
+
+def plan_segments(counts) -> tuple[list[int], list[int]] | None:
+    """Rows of at least two segments' length are cut into segments of ``SEGMENT`` tokens, every other row is one segment:
+    (first token of every segment plus the end, the row of every segment), or None when no row is that long."""
+    if max(counts) < 2 * SEGMENT:
+        return None
+    starts, rows, at = [], [], 0
+    for row, count in enumerate(counts):
+        count = int(count)
+        pieces = max(1, count // SEGMENT) if count >= 2 * SEGMENT else 1
+        for piece in range(pieces):
+            starts.append(at + piece * SEGMENT)
+            rows.append(row)
+        at += count
+    return starts + [at], rows
+
+
+def retention_in_segments(proj: torch.Tensor, k_off: int, q_off: int, v_off: int, decay: torch.Tensor, state: torch.Tensor, slots: torch.Tensor,
+                          seg_start: torch.Tensor, seg_row: torch.Tensor, segments: int, heads: int, n: int, n_padded: int, e: int) -> torch.Tensor:
+    """The retention scan of :func:`state_scan` with long rows cut into segments that are walked side by side: every segment from a
+    zero state, the segments' states joined (``csrc/recurrent.cu``: ``join_segments_kernel``), every segment again from its true
+    start.  Twice the arithmetic for as many times the blocks; the result differs from the one-pass scan by rounding."""
+    require_cuda(proj, decay, state, slots, seg_start, seg_row)
+    per_head = e * n_padded
+    ends = torch.zeros((segments, heads * per_head), dtype=torch.float32, device=proj.device)
+    own = torch.arange(segments, dtype=torch.int32, device=proj.device)
+    state_scan(MODE_RETENTION, proj, k_off, q_off, v_off, proj, 0, 0, decay, decay, None, ends, 0, own, seg_start, segments, heads, heads, n, n_padded, e,
+               states_only=True)
+    check(library("recurrent").hb_join_segments(ptr(ends), ctypes.c_longlong(ends.stride(0)), ptr(state), ctypes.c_longlong(state.stride(0)), i32(0), ptr(slots),
+                                                ptr(seg_start), ptr(seg_row), i32(segments), ptr(decay), i32(heads), i32(per_head), stream_ptr()), "join_segments")
+    return state_scan(MODE_RETENTION, proj, k_off, q_off, v_off, proj, 0, 0, decay, decay, None, ends, 0, own, seg_start, segments, heads, heads, n, n_padded, e)

@@ -202,13 +202,35 @@ class Retention(Branch):
     def kernel_modules(self):
         return [("heads_prepare", {}), ("recurrent", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
 
+    def step_plans(self):
+        """In bfloat16, where bits need not repeat across cuts of the work, a step with a long row walks it in segments side by side."""
+        if self.dtype != torch.bfloat16:
+            return {}
+
+        def plan(rows, packer, host):
+            if "scan_segments" in host:
+                return
+            counts = rows.counts if hasattr(rows, "counts") else [row.count for row in rows]
+            cut = recurrent.plan_segments([int(c) for c in counts])
+            host["scan_segments"] = 0 if cut is None else len(cut[1])
+            if cut is not None:
+                packer.add("scan_seg_start", cut[0])
+                packer.add("scan_seg_row", cut[1])
+
+        return {("scan_segments", recurrent.SEGMENT): plan}
+
     def core(self, proj, col0, step, cache, out, scale):
         k_off, v_off = col0 + self.qk_width, col0 + 2 * self.qk_width
         ops.heads_prepare_wide(proj, col0, k_off, v_off, self.heads, self.heads, self.n, self.e, step.positions, q_out=proj[:, col0:k_off],
                                k_out=proj[:, k_off:v_off], inv_freq=self.position.inv_freq if self.position is not None else None,
                                rot_dims=self.position.dims if self.position is not None else 0, rot_half=True, k_scale=self.n ** -0.5)
-        o = recurrent.state_scan(recurrent.MODE_RETENTION, proj, k_off, col0, v_off, proj, 0, 0, self.decay, self.decay, None, cache.state, 0, cache.slots,
-                                 step.row_start, step.n_rows, self.heads, self.heads, self.n, self.n_padded, self.e)
+        segments = step.host.get("scan_segments", 0) if self.dtype == torch.bfloat16 else 0
+        if segments:
+            o = recurrent.retention_in_segments(proj, k_off, col0, v_off, self.decay, cache.state, cache.slots, step.extra["scan_seg_start"],
+                                                step.extra["scan_seg_row"], segments, self.heads, self.n, self.n_padded, self.e)
+        else:
+            o = recurrent.state_scan(recurrent.MODE_RETENTION, proj, k_off, col0, v_off, proj, 0, 0, self.decay, self.decay, None, cache.state, 0, cache.slots,
+                                     step.row_start, step.n_rows, self.heads, self.heads, self.n, self.n_padded, self.e)
         recurrent.gated_group_norm(o, proj, v_off + self.core_width, None, self.e, False, self.eps, self.dtype, scale=scale, out=out)
 
 

@@ -504,6 +504,35 @@ def test_first_tokens_and_long_decoding(folders, dtype):
     assert rows_over(single, whole, TOLERANCE[dtype]) <= 0.03
 
 
+def test_long_rows_scanned_in_segments(folders):
+    """In bfloat16 a row of 512 tokens or more has its retention scan cut into segments that run side by side and are joined: a
+    prompt of 700 tokens, then decoded tokens that go on from the joined state, then a long portion of one request beside
+    single tokens of two others whose states must stay their own."""
+    from hyperion_b200.engine.batch import StepEntry
+
+    name, vocab = "retention", ALONE["retention"]["vocab"]
+    a, b, c = ids_for(41, 720, vocab), ids_for(42, 40, vocab), ids_for(43, 1300, vocab)
+    want = {"a": plain_logits(folders[name], a), "b": plain_logits(folders[name], b), "c": plain_logits(folders[name], c)}
+    engine = engine_for(folders[name], "bfloat16", max_tokens=4096)
+    got = engine.step([StepEntry("a", a[:700], list(range(700)))]).cpu().numpy().copy()
+    assert engine.runner.last_context.host["scan_segments"] == 2
+    assert_close(got, want["a"][:700], "bfloat16", "a prompt in two segments")
+    for at in range(700, 720):
+        row = engine.step([StepEntry("a", [a[at]], [0])]).cpu().numpy()[0]
+        assert_close(row, want["a"][at], "bfloat16", ("decoded after the joined state", at))
+    engine.finish("a")
+    engine.step([StepEntry("b", b[:30], []), StepEntry("c", c[:100], [])])
+    got = engine.step([StepEntry("b", [b[30]], [0]), StepEntry("c", c[100:1299], list(range(1199))), StepEntry("a", a[:1], [0])]).cpu().numpy().copy()
+    assert engine.runner.last_context.host["scan_segments"] == 1 + 4 + 1
+    assert_close(got[0], want["b"][30], "bfloat16", "a single token beside a long portion")
+    assert_close(got[1:1200], want["c"][100:1299], "bfloat16", "a long portion that goes on from a state")
+    assert_close(got[1200], want["a"][0], "bfloat16", "a first token beside a long portion")
+    got = engine.step([StepEntry("b", [b[31]], [0]), StepEntry("c", [c[1299]], [0])]).cpu().numpy()
+    assert_close(got[0], want["b"][31], "bfloat16")
+    assert_close(got[1], want["c"][1299], "bfloat16", "decoded after four joined segments")
+    engine.check()
+
+
 @pytest.mark.parametrize("name", sorted(CONFIGS))
 def test_greedy_generation_through_the_scheduler(folders, name):
     from hyperion_b200.sampling import SamplingParams
