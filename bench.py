@@ -564,6 +564,12 @@ def mirovik_kernels(size: dict, measured: dict) -> dict:
                                             len(counts), heads, heads, n, n, e)
         report(f"retention.scan/{shape}", timed(scan), 4 * (tokens * (2 * heads * n + 2 * heads * e) + 2 * len(counts) * heads * e * n), fp32_flops=4.0 * tokens * heads * n * e)
         o = scan()
+        cut = recurrent.plan_segments(counts)
+        if cut is not None:  # the long row in segments side by side, as the bfloat16 engine walks it
+            seg_start, seg_row = torch.tensor(cut[0], dtype=torch.int32, device=dev), torch.tensor(cut[1], dtype=torch.int32, device=dev)
+            report(f"retention.scan_in_segments/{shape}", timed(lambda: recurrent.retention_in_segments(proj, k_off, 0, v_off, decay, state, slots, seg_start, seg_row,
+                                                                                                         len(cut[1]), heads, n, n, e)),
+                   4 * (tokens * (2 * heads * n + 2 * heads * e) + 2 * len(counts) * heads * e * n), fp32_flops=8.0 * tokens * heads * n * e)
         gated = torch.empty(tokens, heads * e, dtype=torch.bfloat16, device=dev)
         report(f"retention.gated_norm/{shape}", timed(lambda: recurrent.gated_group_norm(o, proj, g_off, None, e, False, 1e-6, torch.bfloat16, out=gated)),
                tokens * heads * e * (4 + 4 + 2))
@@ -585,6 +591,10 @@ def mirovik_kernels(size: dict, measured: dict) -> dict:
         report(f"selective.scan/{shape}", timed(lambda: recurrent.selective_scan(x, dt, bc, rank, rank + states, a, skip, gate, channels, s_state, 0, slots, row_start,
                                                                                  len(counts), states, states, torch.bfloat16)),
                4 * (tokens * (3 * channels + 2 * states) + 2 * len(counts) * channels * states) + 2 * tokens * channels, fp32_flops=6.0 * tokens * channels * states)
+        if cut is not None:
+            report(f"selective.scan_in_segments/{shape}", timed(lambda: recurrent.selective_in_segments(x, dt, bc, rank, rank + states, a, skip, gate, channels, s_state, slots,
+                                                                                                         seg_start, seg_row, len(cut[1]), states, states, torch.bfloat16)),
+                   4 * (tokens * (3 * channels + 2 * states) + 2 * len(counts) * channels * states) + 2 * tokens * channels, fp32_flops=12.0 * tokens * channels * states)
         w_conv, b_conv = torch.randn(channels, 4, device=dev) * 0.3, torch.zeros(channels, device=dev)
         c_state = torch.zeros(len(counts), 3 * channels, device=dev)
         report(f"selective.conv/{shape}", timed(lambda: recurrent.causal_conv_silu(gate, 0, w_conv, b_conv, c_state, 0, slots, token_row, row_start)), tokens * channels * 8)

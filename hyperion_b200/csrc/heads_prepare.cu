@@ -183,11 +183,12 @@ __global__ void __launch_bounds__(THREADS) heads_prepare_wide_kernel(
 namespace {
 constexpr int TOKEN_THREADS = 256, MAX_PAIRS = 128;
 
+// Heads first .. first + heads - 1 of a projection whose head 0 starts at `all`.
 template <typename TO, typename Place>
-__device__ __forceinline__ void prepare_heads_of_token(const float* all, int heads, int head_dim, const float* w, float inv, float post, int pairs,
+__device__ __forceinline__ void prepare_heads_of_token(const float* all, int first, int heads, int head_dim, const float* w, float inv, float post, int pairs,
                                                        int rot_half, const float* cs, const float* sn, Place place) {
     for (int item = threadIdx.x; item < heads * pairs; item += TOKEN_THREADS) {
-        const int head = item / pairs, i = item - head * pairs;
+        const int head = first + item / pairs, i = item % pairs;
         const int a = rot_half ? i : 2 * i, b = rot_half ? i + pairs : 2 * i + 1;
         const float* p = all + (size_t)head * head_dim;
         const float* wh = w ? w + (size_t)head * head_dim : nullptr;
@@ -199,7 +200,7 @@ __device__ __forceinline__ void prepare_heads_of_token(const float* all, int hea
     }
     const int rest = head_dim - 2 * pairs;
     for (int item = threadIdx.x; item < heads * rest; item += TOKEN_THREADS) {
-        const int head = item / rest, d = 2 * pairs + (item - head * rest);
+        const int head = first + item / rest, d = 2 * pairs + item % rest;
         TO* dst = place(head);
         if (!dst) continue;
         dst[d] = from_float<TO>(all[(size_t)head * head_dim + d] * inv * (w ? w[(size_t)head * head_dim + d] : 1.f) * post);
@@ -242,21 +243,26 @@ __global__ void __launch_bounds__(TOKEN_THREADS) heads_prepare_token_kernel(
         }
         slot = pos - block * page_size;
     }
-    prepare_heads_of_token<TO>(row + q_off, q_heads, head_dim, q_norm, inv_q, 1.f, pairs, rot_half, cs, sn,
+    // a step of few tokens spreads a token's heads over several blocks (blockIdx.y of gridDim.y); each takes the sums for itself
+    const int parts = gridDim.y, part = blockIdx.y;
+    const int q_each = (q_heads + parts - 1) / parts, k_each = (kv_heads + parts - 1) / parts;
+    const int q_first = min(q_heads, part * q_each), q_count = min(q_heads, q_first + q_each) - q_first;
+    const int k_first = min(kv_heads, part * k_each), k_count = min(kv_heads, k_first + k_each) - k_first;
+    prepare_heads_of_token<TO>(row + q_off, q_first, q_count, head_dim, q_norm, inv_q, 1.f, pairs, rot_half, cs, sn,
                                [&](int head) { return q_out + (size_t)t * q_out_stride + (size_t)head * head_dim; });
     if (k_cache) {
         TO* key_page = page >= 0 ? k_cache + (size_t)page * page_stride + (size_t)slot * token_stride : nullptr;
-        prepare_heads_of_token<TO>(row + k_off, kv_heads, head_dim, k_norm, inv_k, k_scale, pairs, rot_half, cs, sn,
+        prepare_heads_of_token<TO>(row + k_off, k_first, k_count, head_dim, k_norm, inv_k, k_scale, pairs, rot_half, cs, sn,
                                    [&](int head) { return key_page ? key_page + (size_t)head * head_stride : nullptr; });
         if (page >= 0) {
             TO* value_page = v_cache + (size_t)page * page_stride + (size_t)slot * token_stride;
-            for (int item = threadIdx.x; item < kv_heads * v_dim; item += TOKEN_THREADS) {
-                const int head = item / v_dim, d = item - head * v_dim;
-                value_page[(size_t)head * head_stride + d] = from_float<TO>(row[v_off + item]);
+            for (int item = threadIdx.x; item < k_count * v_dim; item += TOKEN_THREADS) {
+                const int head = k_first + item / v_dim, d = item % v_dim;
+                value_page[(size_t)head * head_stride + d] = from_float<TO>(row[v_off + (size_t)head * v_dim + d]);
             }
         }
     } else {
-        prepare_heads_of_token<TO>(row + k_off, kv_heads, head_dim, k_norm, inv_k, k_scale, pairs, rot_half, cs, sn,
+        prepare_heads_of_token<TO>(row + k_off, k_first, k_count, head_dim, k_norm, inv_k, k_scale, pairs, rot_half, cs, sn,
                                    [&](int head) { return k_out + (size_t)t * k_out_stride + (size_t)head * head_dim; });
     }
 }
@@ -274,15 +280,19 @@ HB_EXPORT int hb_heads_prepare_wide(const float* x, int tokens, int stride, int 
     if (head_dim <= 0 || v_dim <= 0 || rot_dims < 0 || rot_dims > head_dim || (rot_dims & 1) || !q_out || (!k_cache && !k_out)) return HB_UNSUPPORTED_SIZE;
     const int heads = q_heads + kv_heads + (k_cache ? kv_heads : 0);
     if (heads <= 0 || heads > 65535) return HB_UNSUPPORTED_SIZE;
-    if ((norm_whole || (!q_norm && !k_norm)) && rot_dims / 2 <= MAX_PAIRS) {  // one block per token
+    if ((norm_whole || (!q_norm && !k_norm)) && rot_dims / 2 <= MAX_PAIRS) {  // one block per token, several when the tokens are few
+        const int most = q_heads > kv_heads ? q_heads : kv_heads;
+        int parts = tokens >= 256 ? 1 : 256 / tokens;
+        parts = parts > most ? most : (parts > 16 ? 16 : parts);
+        const dim3 token_grid(tokens, parts < 1 ? 1 : parts);
         if (out_is_bf16)
-            heads_prepare_token_kernel<<<tokens, TOKEN_THREADS, 0, stream>>>(x, stride, q_off, k_off, v_off, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, eps,
+            heads_prepare_token_kernel<<<token_grid, TOKEN_THREADS, 0, stream>>>(x, stride, q_off, k_off, v_off, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, eps,
                                                                              inv_freq, rot_dims, rot_half, positions, k_scale, (__nv_bfloat16*)q_out, q_out_stride,
                                                                              (__nv_bfloat16*)k_out, k_out_stride, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache,
                                                                              (size_t)page_stride, (size_t)head_stride, token_stride, block_table, table_width,
                                                                              token_row, page_size, pages, status);
         else
-            heads_prepare_token_kernel<<<tokens, TOKEN_THREADS, 0, stream>>>(x, stride, q_off, k_off, v_off, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, eps,
+            heads_prepare_token_kernel<<<token_grid, TOKEN_THREADS, 0, stream>>>(x, stride, q_off, k_off, v_off, q_heads, kv_heads, head_dim, v_dim, q_norm, k_norm, eps,
                                                                              inv_freq, rot_dims, rot_half, positions, k_scale, (float*)q_out, q_out_stride,
                                                                              (float*)k_out, k_out_stride, (float*)k_cache, (float*)v_cache, (size_t)page_stride,
                                                                              (size_t)head_stride, token_stride, block_table, table_width, token_row, page_size,

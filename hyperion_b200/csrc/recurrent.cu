@@ -437,9 +437,10 @@ struct SelectiveArgs {
     int state_off;
     const int* slots;
     const int* row_start;
-    void* out;           // [tokens, out_stride]
+    void* out;           // [tokens, out_stride], or null: only the states are wanted
     int out_stride;
     int inner, n, n_padded;
+    float* dt_sums;      // [rows, inner] or null: the sum of a row's steps per channel (what joins segments scanned side by side)
 };
 
 template <int NG, typename TO>
@@ -503,6 +504,7 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const SelectiveArgs
         }
     };
 
+    float dt_total = 0.f;
     prefetch(t0);
     publish(0);
     __syncthreads();
@@ -514,6 +516,7 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const SelectiveArgs
         for (int j = 0; j < count; ++j) {
             const float dt = sdt[buffer][j][cw], xv = sx[buffer][j][cw];
             const float dx = dt * xv;
+            dt_total += dt;
             float part[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
             for (int r = 0; r < NG; ++r) {
@@ -529,7 +532,7 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const SelectiveArgs
             float y = (part[0] + part[1]) + (part[2] + part[3]);
 #pragma unroll
             for (int offset = 1; offset < LPC; offset <<= 1) y += __shfl_xor_sync(0xffffffffu, y, offset);
-            if (l == 0 && owns) {
+            if (l == 0 && owns && a.out) {
                 const float result = fmaf(skip, xv, y) * sz[buffer][j][cw];
                 reinterpret_cast<TO*>(a.out)[(size_t)(first + j) * a.out_stride + channel] = from_float<TO>(result);
             }
@@ -543,6 +546,7 @@ __global__ void __launch_bounds__(128) selective_scan_kernel(const SelectiveArgs
         const int base = 4 * (LPC * r + l);
         if (owns && base < a.n_padded) *reinterpret_cast<float4*>(kept + base) = make_float4(s[r][0], s[r][1], s[r][2], s[r][3]);
     }
+    if (a.dt_sums && l == 0 && owns) a.dt_sums[(size_t)row * a.inner + channel] = dt_total;
 }
 
 template <typename TO>
@@ -563,12 +567,12 @@ int launch_selective(const SelectiveArgs& a, int rows, cudaStream_t stream) {
 HB_EXPORT int hb_selective_scan(const float* x, int x_stride, const float* dt, int dt_stride, const float* bc, int bc_stride, int b_off, int c_off,
                                 const float* a, const float* skip, const float* gate, int gate_stride, int gate_off, float* state,
                                 long long slot_stride, int state_off, const int* slots, const int* row_start, void* out, int out_is_bf16,
-                                int out_stride, int rows, int inner, int n, int n_padded, cudaStream_t stream) {
+                                int out_stride, int rows, int inner, int n, int n_padded, float* dt_sums, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (n <= 0 || n > 256 || inner <= 0 || rows > 65535) return HB_UNSUPPORTED_SIZE;
     if (n_padded < n || (n_padded & 3) || (state_off & 3) || (slot_stride & 3) || (((uintptr_t)state) & 15)) return HB_BAD_ARGUMENT;
     const SelectiveArgs args{x, x_stride, dt, dt_stride, bc, bc_stride, b_off, c_off, a, skip, gate, gate_stride, gate_off, state, (size_t)slot_stride,
-                             state_off, slots, row_start, out, out_stride, inner, n, n_padded};
+                             state_off, slots, row_start, out, out_stride, inner, n, n_padded, dt_sums};
     return out_is_bf16 ? launch_selective<__nv_bfloat16>(args, rows, stream) : launch_selective<float>(args, rows, stream);
 }
 
@@ -614,5 +618,42 @@ HB_EXPORT int hb_join_segments(float* ends, long long end_stride, float* state, 
     const int entries = heads * per_head;
     join_segments_kernel<<<(entries + 255) / 256, 256, 0, stream>>>(ends, (size_t)end_stride, state, (size_t)slot_stride, state_off, slots, seg_start, seg_row,
                                                                  segments, decay, per_head, entries);
+    return launch_status();
+}
+
+
+// The same joining for the selective scan, whose decay differs per channel and state entry: over a segment it is exp(A[c, i] * the sum
+// of the channel's steps), which the first pass leaves in dt_sums [segments, inner].
+namespace {
+__global__ void join_selective_segments_kernel(float* __restrict__ ends, size_t end_stride, float* __restrict__ state, size_t slot_stride, int state_off,
+                                               const int* __restrict__ slots, const int* __restrict__ seg_row, int segments, const float* __restrict__ a,
+                                               const float* __restrict__ dt_sums, int inner, int n, int n_padded) {
+    const int entry = blockIdx.x * blockDim.x + threadIdx.x;
+    if (entry >= inner * n_padded) return;
+    const int channel = entry / n_padded, i = entry - channel * n_padded;
+    const float rate = i < n ? a[(size_t)channel * n + i] : 0.f;
+    int j = 0;
+    while (j < segments) {
+        const int row = seg_row[j];
+        float* kept = state + (size_t)slots[row] * slot_stride + state_off + entry;
+        float s = *kept;
+        for (; j < segments && seg_row[j] == row; ++j) {
+            const float added = ends[(size_t)j * end_stride + entry];
+            ends[(size_t)j * end_stride + entry] = s;
+            s = fmaf(expf(rate * dt_sums[(size_t)j * inner + channel]), s, added);
+        }
+        *kept = s;
+    }
+}
+}  // namespace
+
+HB_EXPORT int hb_join_selective_segments(float* ends, long long end_stride, float* state, long long slot_stride, int state_off, const int* slots,
+                                         const int* seg_row, int segments, const float* a, const float* dt_sums, int inner, int n, int n_padded,
+                                         cudaStream_t stream) {
+    if (segments <= 0) return 0;
+    if (inner <= 0 || n <= 0 || n_padded < n) return HB_BAD_ARGUMENT;
+    const int entries = inner * n_padded;
+    join_selective_segments_kernel<<<(entries + 255) / 256, 256, 0, stream>>>(ends, (size_t)end_stride, state, (size_t)slot_stride, state_off, slots, seg_row,
+                                                                           segments, a, dt_sums, inner, n, n_padded);
     return launch_status();
 }

@@ -82,21 +82,23 @@ def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, gate_off: int, weight:
 
 def selective_scan(x: torch.Tensor, dt: torch.Tensor, bc: torch.Tensor, b_off: int, c_off: int, a: torch.Tensor, skip: torch.Tensor, gate: torch.Tensor,
                    gate_off: int, state: torch.Tensor, state_off: int, slots: torch.Tensor, row_start: torch.Tensor, rows: int, n: int, n_padded: int,
-                   out_dtype: torch.dtype) -> torch.Tensor:
+                   out_dtype: torch.dtype, states_only: bool = False, dt_sums: torch.Tensor | None = None) -> torch.Tensor | None:
     """The recurrence with a decay per channel and state entry: per channel c, S[c] <- exp(dt_c A[c]) S[c] + dt_c x_c B,
     y_c = (S[c] . C + D_c x_c) silu(z_c), with dt = softplus(``dt``), B and C the columns ``b_off ..`` and ``c_off ..`` of ``bc``,
     A = ``a`` [inner, n] (negative), D = ``skip``, z the columns ``gate_off ..`` of ``gate``; every row's tokens walk from and
-    into its slot of ``state``.  Returns [tokens, inner] in ``out_dtype``."""
-    require_cuda(x, dt, bc, a, skip, gate, state, slots, row_start)
-    _floats(x, dt, bc, a, skip, gate, state)
+    into its slot of ``state``.  Returns [tokens, inner] in ``out_dtype`` (nothing with ``states_only``).  ``dt_sums`` [rows, inner] float
+    receives the sum of every row's steps per channel."""
+    require_cuda(x, dt, bc, a, skip, gate, state, slots, row_start, dt_sums)
+    _floats(x, dt, bc, a, skip, gate, state, dt_sums)
     tokens, inner = x.shape
     if a.shape != (inner, n) or not a.is_contiguous() or skip.numel() != inner or dt.shape != x.shape:
         raise KernelError("selective_scan: A is [inner, n], D [inner], the steps [tokens, inner]")
-    out = torch.empty((tokens, inner), dtype=out_dtype, device=x.device)
+    out = None if states_only else torch.empty((tokens, inner), dtype=out_dtype, device=x.device)
     check(library("recurrent").hb_selective_scan(ptr(x), i32(x.stride(0)), ptr(dt), i32(dt.stride(0)), ptr(bc), i32(bc.stride(0)), i32(b_off), i32(c_off),
                                                  ptr(a), ptr(skip), ptr(gate), i32(gate.stride(0)), i32(gate_off), ptr(state), ctypes.c_longlong(state.stride(0)),
-                                                 i32(state_off), ptr(slots), ptr(row_start), ptr(out), i32(is_bf16(out)), i32(out.stride(0)), i32(rows),
-                                                 i32(inner), i32(n), i32(n_padded), stream_ptr()), "selective_scan")
+                                                 i32(state_off), ptr(slots), ptr(row_start), ptr(out), i32(is_bf16(out) if out is not None else 0),
+                                                 i32(out.stride(0) if out is not None else 0), i32(rows), i32(inner), i32(n), i32(n_padded), ptr(dt_sums),
+                                                 stream_ptr()), "selective_scan")
     return out
 
 
@@ -133,3 +135,39 @@ def retention_in_segments(proj: torch.Tensor, k_off: int, q_off: int, v_off: int
     check(library("recurrent").hb_join_segments(ptr(ends), ctypes.c_longlong(ends.stride(0)), ptr(state), ctypes.c_longlong(state.stride(0)), i32(0), ptr(slots),
                                                 ptr(seg_start), ptr(seg_row), i32(segments), ptr(decay), i32(heads), i32(per_head), stream_ptr()), "join_segments")
     return state_scan(MODE_RETENTION, proj, k_off, q_off, v_off, proj, 0, 0, decay, decay, None, ends, 0, own, seg_start, segments, heads, heads, n, n_padded, e)
+
+
+def selective_in_segments(x: torch.Tensor, dt: torch.Tensor, bc: torch.Tensor, b_off: int, c_off: int, a: torch.Tensor, skip: torch.Tensor,
+                          gate: torch.Tensor, gate_off: int, state: torch.Tensor, slots: torch.Tensor, seg_start: torch.Tensor, seg_row: torch.Tensor,
+                          segments: int, n: int, n_padded: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """:func:`selective_scan` with long rows cut into segments that are walked side by side (see :func:`retention_in_segments`); a
+    segment's decay per channel and state entry is exp(A times the sum of the channel's steps over the segment)."""
+    inner = x.shape[1]
+    ends = torch.zeros((segments, inner * n_padded), dtype=torch.float32, device=x.device)
+    sums = torch.empty((segments, inner), dtype=torch.float32, device=x.device)
+    own = torch.arange(segments, dtype=torch.int32, device=x.device)
+    selective_scan(x, dt, bc, b_off, c_off, a, skip, gate, gate_off, ends, 0, own, seg_start, segments, n, n_padded, out_dtype, states_only=True, dt_sums=sums)
+    check(library("recurrent").hb_join_selective_segments(ptr(ends), ctypes.c_longlong(ends.stride(0)), ptr(state), ctypes.c_longlong(state.stride(0)), i32(0),
+                                                          ptr(slots), ptr(seg_row), i32(segments), ptr(a), ptr(sums), i32(inner), i32(n), i32(n_padded),
+                                                          stream_ptr()), "join_selective_segments")
+    return selective_scan(x, dt, bc, b_off, c_off, a, skip, gate, gate_off, ends, 0, own, seg_start, segments, n, n_padded, out_dtype)
+
+
+def segment_planner(dtype: torch.dtype) -> dict:
+    """The step planner of mixers that scan long rows in segments: in bfloat16, where bits need not repeat across cuts of the work, a
+    step with a row of at least two segments' length gets ``scan_seg_start`` and ``scan_seg_row`` among its arrays and their number in
+    ``step.host["scan_segments"]`` (0 otherwise)."""
+    if dtype != torch.bfloat16:
+        return {}
+
+    def plan(rows, packer, host):
+        if "scan_segments" in host:
+            return
+        counts = rows.counts if hasattr(rows, "counts") else [row.count for row in rows]
+        cut = plan_segments([int(c) for c in counts])
+        host["scan_segments"] = 0 if cut is None else len(cut[1])
+        if cut is not None:
+            packer.add("scan_seg_start", cut[0])
+            packer.add("scan_seg_row", cut[1])
+
+    return {("scan_segments", SEGMENT): plan}

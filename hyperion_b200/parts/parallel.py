@@ -203,21 +203,7 @@ class Retention(Branch):
         return [("heads_prepare", {}), ("recurrent", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
 
     def step_plans(self):
-        """In bfloat16, where bits need not repeat across cuts of the work, a step with a long row walks it in segments side by side."""
-        if self.dtype != torch.bfloat16:
-            return {}
-
-        def plan(rows, packer, host):
-            if "scan_segments" in host:
-                return
-            counts = rows.counts if hasattr(rows, "counts") else [row.count for row in rows]
-            cut = recurrent.plan_segments([int(c) for c in counts])
-            host["scan_segments"] = 0 if cut is None else len(cut[1])
-            if cut is not None:
-                packer.add("scan_seg_start", cut[0])
-                packer.add("scan_seg_row", cut[1])
-
-        return {("scan_segments", recurrent.SEGMENT): plan}
+        return recurrent.segment_planner(self.dtype)
 
     def core(self, proj, col0, step, cache, out, scale):
         k_off, v_off = col0 + self.qk_width, col0 + 2 * self.qk_width

@@ -197,6 +197,9 @@ class SelectiveScanMixer(Mixer):
     def kernel_modules(self):
         return [("recurrent", {}), ("sgemm_f32", {}) if self.dtype == torch.float32 else ("gemm_tcgen05", {})]
 
+    def step_plans(self):
+        return recurrent.segment_planner(self.dtype)
+
     def forward(self, x, step, cache, own_cache):
         if cache is None or not own_cache:
             raise ValueError("the selective scan keeps a state per request; the schedule gave it none")
@@ -206,8 +209,13 @@ class SelectiveScanMixer(Mixer):
         recurrent.conv_state_update(proj, 0, self.inner, self.taps, state, self.conv_off, slots, step.row_start, rows)
         dbc = ops.linear(conv, self.w_x, None, torch.float32)  # [d | B | C]
         dt = ops.linear(dbc[:, : self.rank], self.w_dt, self.b_dt, torch.float32)
-        y = recurrent.selective_scan(conv, dt, dbc, self.rank, self.rank + self.n, self.a, self.skip, proj, self.inner, state, 0, slots,
-                                     step.row_start, rows, self.n, self.n_padded, self.dtype)
+        segments = step.host.get("scan_segments", 0) if self.dtype == torch.bfloat16 else 0
+        if segments:  # a long row: its segments side by side, joined by a second pass
+            y = recurrent.selective_in_segments(conv, dt, dbc, self.rank, self.rank + self.n, self.a, self.skip, proj, self.inner, state, slots,
+                                                step.extra["scan_seg_start"], step.extra["scan_seg_row"], segments, self.n, self.n_padded, self.dtype)
+        else:
+            y = recurrent.selective_scan(conv, dt, dbc, self.rank, self.rank + self.n, self.a, self.skip, proj, self.inner, state, 0, slots,
+                                         step.row_start, rows, self.n, self.n_padded, self.dtype)
         return ops.linear(y, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
 
 

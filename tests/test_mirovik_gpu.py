@@ -93,6 +93,8 @@ CONFIGS = {
 }
 ALONE = {
     "attention": document(48, 97, [layer("parallel", parallel(left(4, 2, 24, 12, 30, 8, scale=0.25), right(1, 8, 8, [0.9]), 1.0, 0.0))], scale=0.4),
+    # heads of 128 for keys and values alike: in bfloat16 the tensor-core kernels read the pages, with the bias table as an argument
+    "attention_wide": document(64, 97, [layer("parallel", parallel(left(2, 1, 128, 128, 40, 8), right(1, 8, 8, [0.9]), 1.0, 0.0))], scale=0.5),
     "retention": document(48, 97, [layer("parallel", parallel(left(1, 1, 8, 8, 9, 4), right(3, 20, 28, [0.9, 0.99, 0.999], rot=12), 0.0, 1.0))]),
     "retention_wide": document(40, 61, [layer("parallel", parallel(left(1, 1, 8, 8, 9, 4), right(1, 136, 8, [0.97], rot=136), 0.0, 1.0))]),
     "selective": document(48, 97, [layer("mamba1", selective(88, 24, 5, 4))]),
@@ -504,13 +506,40 @@ def test_first_tokens_and_long_decoding(folders, dtype):
     assert rows_over(single, whole, TOLERANCE[dtype]) <= 0.03
 
 
-def test_long_rows_scanned_in_segments(folders):
-    """In bfloat16 a row of 512 tokens or more has its retention scan cut into segments that run side by side and are joined: a
-    prompt of 700 tokens, then decoded tokens that go on from the joined state, then a long portion of one request beside
-    single tokens of two others whose states must stay their own."""
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_keys_far_beyond_the_last_bucket_in_the_tensor_core_kernels(folders, dtype):
+    """Heads of 128 and a bias that ends at distance 40: in a prompt of 450 tokens most key tiles lie wholly in the last bucket
+    (the prompt kernel adds their bias as one shift of the tile), the tiles near the diagonal look every score's bias up; the
+    tail is decoded token by token through the split-key kernel."""
     from hyperion_b200.engine.batch import StepEntry
 
-    name, vocab = "retention", ALONE["retention"]["vocab"]
+    name, vocab = "attention_wide", ALONE["attention_wide"]["vocab"]
+    ids = ids_for(77, 450, vocab)
+    want = plain_logits(folders[name], ids)
+    engine = engine_for(folders[name], dtype)
+    whole = run_cut(engine, "w", ids, [len(ids)])
+    assert_close(whole, want, dtype, "whole")
+    got = [engine.step([StepEntry("d", ids[:300], list(range(300)))]).cpu().numpy().copy()]
+    got.append(engine.step([StepEntry("d", ids[300:420], list(range(120)))]).cpu().numpy().copy())
+    for at in range(420, 450):
+        got.append(engine.step([StepEntry("d", [ids[at]], [0])]).cpu().numpy().copy())
+    engine.finish("d")
+    engine.check()
+    assert_close(np.concatenate(got), want, dtype, "two portions and a decoded tail")
+    # the last bucket's bias matters: without it the plain logits move by many tolerances
+    config, weights = plain.read_model_folder(folders[name])
+    weights["l0.mix.left.rel"][-1] = 0
+    assert relative_error(plain.forward(config, weights, ids).numpy()[-50:], want[-50:]) > 20 * TOLERANCE["bfloat16"]
+
+
+@pytest.mark.parametrize("name", ["retention", "selective"])
+def test_long_rows_scanned_in_segments(folders, name):
+    """In bfloat16 a row of 512 tokens or more has its scan (retention, selective) cut into segments that run side by side and are
+    joined: a prompt of 700 tokens, then decoded tokens that go on from the joined state, then a long portion of one request
+    beside single tokens of two others whose states must stay their own."""
+    from hyperion_b200.engine.batch import StepEntry
+
+    vocab = ALONE[name]["vocab"]
     a, b, c = ids_for(41, 720, vocab), ids_for(42, 40, vocab), ids_for(43, 1300, vocab)
     want = {"a": plain_logits(folders[name], a), "b": plain_logits(folders[name], b), "c": plain_logits(folders[name], c)}
     engine = engine_for(folders[name], "bfloat16", max_tokens=4096)
