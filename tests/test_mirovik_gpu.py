@@ -526,10 +526,10 @@ def test_keys_far_beyond_the_last_bucket_in_the_tensor_core_kernels(folders, dty
     engine.finish("d")
     engine.check()
     assert_close(np.concatenate(got), want, dtype, "two portions and a decoded tail")
-    # the last bucket's bias matters: without it the plain logits move by many tolerances
+    # the last bucket's bias matters: without it the plain logits of the late rows are off by several tolerances
     config, weights = plain.read_model_folder(folders[name])
     weights["l0.mix.left.rel"][-1] = 0
-    assert relative_error(plain.forward(config, weights, ids).numpy()[-50:], want[-50:]) > 20 * TOLERANCE["bfloat16"]
+    assert rows_over(plain.forward(config, weights, ids).numpy()[-50:], want[-50:], 2 * TOLERANCE["bfloat16"]) > 0.5
 
 
 @pytest.mark.parametrize("name", ["retention", "selective"])
