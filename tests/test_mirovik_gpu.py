@@ -172,6 +172,10 @@ def folders(tmp_path_factory):
         weights = make_weights(doc, 11 + index)
         if name == "attention":
             align_keys_with_queries(doc, weights)
+        if name == "attention_wide":  # a flat attention that favours the keys of the last bucket: what the far tiles add decides the result
+            weights["l0.mix.left.rel"][-1] = 4.0
+            for norm in ("l0.mix.left.q.norm", "l0.mix.left.k.norm"):
+                weights[norm] = (0.25 * weights[norm].float()).to(torch.bfloat16)
         write_file(folder / "model.safetensors", weights)
         made[name] = folder
     return made
@@ -529,7 +533,7 @@ def test_keys_far_beyond_the_last_bucket_in_the_tensor_core_kernels(folders, dty
     # the last bucket's bias matters: without it the plain logits of the late rows are off by several tolerances
     config, weights = plain.read_model_folder(folders[name])
     weights["l0.mix.left.rel"][-1] = 0
-    assert rows_over(plain.forward(config, weights, ids).numpy()[-50:], want[-50:], 2 * TOLERANCE["bfloat16"]) > 0.5
+    assert rows_over(plain.forward(config, weights, ids).numpy()[-50:], want[-50:], 2 * TOLERANCE["bfloat16"]) > 0.9
 
 
 @pytest.mark.parametrize("name", ["retention", "selective"])
