@@ -95,6 +95,8 @@ ALONE = {
     "attention": document(48, 97, [layer("parallel", parallel(left(4, 2, 24, 12, 30, 8, scale=0.25), right(1, 8, 8, [0.9]), 1.0, 0.0))], scale=0.4),
     # heads of 128 for keys and values alike: in bfloat16 the tensor-core kernels read the pages, with the bias table as an argument
     "attention_wide": document(64, 97, [layer("parallel", parallel(left(2, 1, 128, 128, 40, 8), right(1, 8, 8, [0.9]), 1.0, 0.0))], scale=0.5),
+    # heads of 192: the TMA-fed tile kernel serves prompt portions too
+    "attention_192": document(64, 97, [layer("parallel", parallel(left(2, 2, 192, 192, 40, 8), right(1, 8, 8, [0.9]), 1.0, 0.0))], scale=0.5),
     "retention": document(48, 97, [layer("parallel", parallel(left(1, 1, 8, 8, 9, 4), right(3, 20, 28, [0.9, 0.99, 0.999], rot=12), 0.0, 1.0))]),
     "retention_wide": document(40, 61, [layer("parallel", parallel(left(1, 1, 8, 8, 9, 4), right(1, 136, 8, [0.97], rot=136), 0.0, 1.0))]),
     "selective": document(48, 97, [layer("mamba1", selective(88, 24, 5, 4))]),
@@ -172,7 +174,7 @@ def folders(tmp_path_factory):
         weights = make_weights(doc, 11 + index)
         if name == "attention":
             align_keys_with_queries(doc, weights)
-        if name == "attention_wide":  # a flat attention that favours the keys of the last bucket: what the far tiles add decides the result
+        if name in ("attention_wide", "attention_192"):  # a flat attention that favours the keys of the last bucket: what the far tiles add decides the result
             weights["l0.mix.left.rel"][-1] = 4.0
             for norm in ("l0.mix.left.q.norm", "l0.mix.left.k.norm"):
                 weights[norm] = (0.25 * weights[norm].float()).to(torch.bfloat16)
@@ -511,13 +513,14 @@ def test_first_tokens_and_long_decoding(folders, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_keys_far_beyond_the_last_bucket_in_the_tensor_core_kernels(folders, dtype):
-    """Heads of 128 and a bias that ends at distance 40: in a prompt of 450 tokens most key tiles lie wholly in the last bucket
-    (the prompt kernel adds their bias as one shift of the tile), the tiles near the diagonal look every score's bias up; the
-    tail is decoded token by token through the split-key kernel."""
+@pytest.mark.parametrize("name", ["attention_wide", "attention_192"])
+def test_keys_far_beyond_the_last_bucket_in_the_tensor_core_kernels(folders, name, dtype):
+    """Heads of 128 (and of 192) and a bias that ends at distance 40: in a prompt of 450 tokens most key tiles lie wholly in the last
+    bucket (the tcgen05 prompt kernel adds their bias as one shift of the tile), the tiles near the diagonal look every score's bias
+    up; the tail is decoded token by token through the split-key kernel."""
     from hyperion_b200.engine.batch import StepEntry
 
-    name, vocab = "attention_wide", ALONE["attention_wide"]["vocab"]
+    vocab = ALONE[name]["vocab"]
     ids = ids_for(77, 450, vocab)
     want = plain_logits(folders[name], ids)
     engine = engine_for(folders[name], dtype)
