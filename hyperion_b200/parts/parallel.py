@@ -210,7 +210,11 @@ class Retention(Branch):
         ops.heads_prepare_wide(proj, col0, k_off, v_off, self.heads, self.heads, self.n, self.e, step.positions, q_out=proj[:, col0:k_off],
                                k_out=proj[:, k_off:v_off], inv_freq=self.position.inv_freq if self.position is not None else None,
                                rot_dims=self.position.dims if self.position is not None else 0, rot_half=True, k_scale=self.n ** -0.5)
-        segments = step.host.get("scan_segments", 0) if self.dtype == torch.bfloat16 else 0
+        # Segments pay while one pass leaves the GPU mostly idle: a row's walk is a chain of dependent steps (0.23 us a token on a
+        # B200) that few blocks share, and cutting it doubles the arithmetic.  Measured at heads of 128 x 128: 64 blocks 482 -> 290 us for
+        # 2,048 tokens, 128 blocks 487 -> 509 us.
+        blocks = self.heads * -(-self.e // 32)
+        segments = step.host.get("scan_segments", 0) if self.dtype == torch.bfloat16 and blocks <= 100 else 0
         if segments:
             o = recurrent.retention_in_segments(proj, k_off, col0, v_off, self.decay, cache.state, cache.slots, step.extra["scan_seg_start"],
                                                 step.extra["scan_seg_row"], segments, self.heads, self.n, self.n_padded, self.e)
