@@ -591,17 +591,32 @@ __global__ void join_segments_kernel(float* __restrict__ ends, size_t end_stride
     const int entry = blockIdx.x * blockDim.x + threadIdx.x;
     if (entry >= entries) return;
     const float log_decay = log2f(decay[entry / per_head]);
+    constexpr int AHEAD = 8;  // what the segments add is asked for before the chain through them starts: one trip to memory, not one per segment
     int j = 0;
     while (j < segments) {
         const int row = seg_row[j];
         float* kept = state + (size_t)slots[row] * slot_stride + state_off + entry;
         float s = *kept;
-        for (; j < segments && seg_row[j] == row; ++j) {
-            const float added = ends[(size_t)j * end_stride + entry];
-            ends[(size_t)j * end_stride + entry] = s;
-            const int length = seg_start[j + 1] - seg_start[j];
-            const float fade = log_decay == 0.f ? 1.f : exp2f((float)length * log_decay);
-            s = fmaf(fade, s, added);
+        while (j < segments && seg_row[j] == row) {
+            float added[AHEAD], fade[AHEAD];
+            int count = 0;
+#pragma unroll
+            for (int k = 0; k < AHEAD; ++k) {
+                if (j + k < segments && seg_row[j + k] == row) {
+                    added[k] = ends[(size_t)(j + k) * end_stride + entry];
+                    const int length = seg_start[j + k + 1] - seg_start[j + k];
+                    fade[k] = log_decay == 0.f ? 1.f : exp2f((float)length * log_decay);
+                    count = k + 1;
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < AHEAD; ++k) {
+                if (k < count) {
+                    ends[(size_t)(j + k) * end_stride + entry] = s;
+                    s = fmaf(fade[k], s, added[k]);
+                }
+            }
+            j += count;
         }
         *kept = s;
     }
@@ -632,15 +647,31 @@ __global__ void join_selective_segments_kernel(float* __restrict__ ends, size_t 
     if (entry >= inner * n_padded) return;
     const int channel = entry / n_padded, i = entry - channel * n_padded;
     const float rate = i < n ? a[(size_t)channel * n + i] : 0.f;
+    constexpr int AHEAD = 8;
     int j = 0;
     while (j < segments) {
         const int row = seg_row[j];
         float* kept = state + (size_t)slots[row] * slot_stride + state_off + entry;
         float s = *kept;
-        for (; j < segments && seg_row[j] == row; ++j) {
-            const float added = ends[(size_t)j * end_stride + entry];
-            ends[(size_t)j * end_stride + entry] = s;
-            s = fmaf(expf(rate * dt_sums[(size_t)j * inner + channel]), s, added);
+        while (j < segments && seg_row[j] == row) {
+            float added[AHEAD], fade[AHEAD];
+            int count = 0;
+#pragma unroll
+            for (int k = 0; k < AHEAD; ++k) {
+                if (j + k < segments && seg_row[j + k] == row) {
+                    added[k] = ends[(size_t)(j + k) * end_stride + entry];
+                    fade[k] = expf(rate * dt_sums[(size_t)(j + k) * inner + channel]);
+                    count = k + 1;
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < AHEAD; ++k) {
+                if (k < count) {
+                    ends[(size_t)(j + k) * end_stride + entry] = s;
+                    s = fmaf(fade[k], s, added[k]);
+                }
+            }
+            j += count;
         }
         *kept = s;
     }
