@@ -2,7 +2,7 @@
 layers that is passed several times.
 
 Every layer is the sandwich arrangement (x <- x + norm_b(mixer(norm_a(x))); x <- x + norm_d(ff(norm_c(x))), the norms' stored
-weights lying around zero) of one of two mixers: attention with a learned distance bias beside retention, summed with a scale
+weights kept as offsets from one) of one of two mixers: attention with a learned distance bias beside retention, summed with a scale
 each (``parallel_mixers`` of ``biased_attention`` and ``retention``), or the selective scan (``mamba1``); with a feed-forward
 without a gate (tanh-form GELU), one of routed experts plus a shared one, or none.  The layers ``loop.start .. loop.stop - 1``
 run ``loop.times`` times in a row with the same weights; every pass is a schedule entry of its own per layer, so it has its own

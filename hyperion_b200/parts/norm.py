@@ -4,7 +4,7 @@ y = x * rsqrt(mean(x^2) + eps) * weight, the weight multiplying after the normal
 (helios/crates/helios-hal/kernels/rmsnorm.cu:22-58); the fused form first adds the pending delta into
 the residual stream (rmsnorm.cu:66-122).  The stream, the sum of squares and the products are float;
 the result is rounded once to the activation type.  Parameters: ``hidden_size``, ``eps``, ``weight_name`` (the tensor's
-name after the prefix, ``weight`` unless stated), ``one_plus`` (the stored weight lies around zero and one is added to it,
+name after the prefix, ``weight`` unless stated), ``one_plus`` (the tensor holds the weight's offset from one, which is added,
 in float, when it is loaded).
 
 ``add_normed`` is the other placement of the same norm: h <- h + norm(y), for blocks that normalise what a sublayer

@@ -159,7 +159,13 @@ class BiasedAttention(Branch):
                                q_norm=self.q_norm, k_norm=self.k_norm, norm_whole=True, eps=self.eps, cache=cache.kv, block_table=cache.block_table,
                                token_row=step.token_row, page_size=cache.page_size)
         if self.fast and fast_attention.takes_distance_bias(self.head_dim, cache.page_size):
-            self._attend_fast(q, step, cache, out=out, bias=self.by_distance_log2)
+            # the tensor-core kernels store rows in 16-byte pieces: columns of a wider buffer whose rows do not start on such a piece
+            # are filled through a buffer of their own
+            direct = out.stride(0) % 8 == 0 and out.data_ptr() % 16 == 0
+            target = out if direct else torch.empty((proj.shape[0], self.core_width), dtype=self.dtype, device=proj.device)
+            self._attend_fast(q, step, cache, out=target, bias=self.by_distance_log2)
+            if not direct:
+                out.copy_(target)
             ops.sigmoid_gate_(out, proj, v_off + self.v_width, scale)
             return
         ops.attention_general(q, self.heads, self.kv_heads, self.head_dim, self.value_dim, cache.kv, cache.block_table, step.token_row, step.positions,

@@ -49,7 +49,7 @@ def unit_rms(x: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def norm_one_plus(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
-    """The layer norms: the stored weight lies around zero and one is added to it."""
+    """The layer norms: the tensor holds the weight's offset from one."""
     return unit_rms(x, eps) * (1.0 + weight)
 
 

@@ -95,8 +95,9 @@ ALONE = {
     "attention": document(48, 97, [layer("parallel", parallel(left(4, 2, 24, 12, 30, 8, scale=0.25), right(1, 8, 8, [0.9]), 1.0, 0.0))], scale=0.4),
     # heads of 128 for keys and values alike: in bfloat16 the tensor-core kernels read the pages, with the bias table as an argument
     "attention_wide": document(64, 97, [layer("parallel", parallel(left(2, 1, 128, 128, 40, 8), right(1, 8, 8, [0.9]), 1.0, 0.0))], scale=0.5),
-    # heads of 192: the TMA-fed tile kernel serves prompt portions too
-    "attention_192": document(64, 97, [layer("parallel", parallel(left(2, 2, 192, 192, 40, 8), right(1, 8, 8, [0.9]), 1.0, 0.0))], scale=0.5),
+    # heads of 192: the TMA-fed tile kernel serves prompt portions too; beside a retention of 6 values, so that the attention's columns
+    # of the buffer both branches fill do not start rows on 16-byte pieces
+    "attention_192": document(64, 97, [layer("parallel", parallel(left(2, 2, 192, 192, 40, 8), right(1, 8, 6, [0.9]), 1.0, 0.0))], scale=0.5),
     "retention": document(48, 97, [layer("parallel", parallel(left(1, 1, 8, 8, 9, 4), right(3, 20, 28, [0.9, 0.99, 0.999], rot=12), 0.0, 1.0))]),
     "retention_wide": document(40, 61, [layer("parallel", parallel(left(1, 1, 8, 8, 9, 4), right(1, 136, 8, [0.97], rot=136), 0.0, 1.0))]),
     "selective": document(48, 97, [layer("mamba1", selective(88, 24, 5, 4))]),
