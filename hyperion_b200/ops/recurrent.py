@@ -82,12 +82,13 @@ def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, gate_off: int, weight:
 
 def selective_scan(x: torch.Tensor, dt: torch.Tensor, bc: torch.Tensor, b_off: int, c_off: int, a: torch.Tensor, skip: torch.Tensor, gate: torch.Tensor,
                    gate_off: int, state: torch.Tensor, state_off: int, slots: torch.Tensor, row_start: torch.Tensor, rows: int, n: int, n_padded: int,
-                   out_dtype: torch.dtype, states_only: bool = False, dt_sums: torch.Tensor | None = None) -> torch.Tensor | None:
+                   out_dtype: torch.dtype, states_only: bool = False, dt_sums: torch.Tensor | None = None, precise: bool = False) -> torch.Tensor | None:
     """The recurrence with a decay per channel and state entry: per channel c, S[c] <- exp(dt_c A[c]) S[c] + dt_c x_c B,
     y_c = (S[c] . C + D_c x_c) silu(z_c), with dt = softplus(``dt``), B and C the columns ``b_off ..`` and ``c_off ..`` of ``bc``,
     A = ``a`` [inner, n] (negative), D = ``skip``, z the columns ``gate_off ..`` of ``gate``; every row's tokens walk from and
     into its slot of ``state``.  Returns [tokens, inner] in ``out_dtype`` (nothing with ``states_only``).  ``dt_sums`` [rows, inner] float
-    receives the sum of every row's steps per channel."""
+    receives the sum of every row's steps per channel.  ``precise``: a token's arithmetic in double precision, rounded to float once
+    (the float32 mode; the state stays float from token to token, so results do not depend on how the rows were cut)."""
     require_cuda(x, dt, bc, a, skip, gate, state, slots, row_start, dt_sums)
     _floats(x, dt, bc, a, skip, gate, state, dt_sums)
     tokens, inner = x.shape
@@ -98,7 +99,7 @@ def selective_scan(x: torch.Tensor, dt: torch.Tensor, bc: torch.Tensor, b_off: i
                                                  ptr(a), ptr(skip), ptr(gate), i32(gate.stride(0)), i32(gate_off), ptr(state), ctypes.c_longlong(state.stride(0)),
                                                  i32(state_off), ptr(slots), ptr(row_start), ptr(out), i32(is_bf16(out) if out is not None else 0),
                                                  i32(out.stride(0) if out is not None else 0), i32(rows), i32(inner), i32(n), i32(n_padded), ptr(dt_sums),
-                                                 stream_ptr()), "selective_scan")
+                                                 i32(1 if precise else 0), stream_ptr()), "selective_scan")
     return out
 
 

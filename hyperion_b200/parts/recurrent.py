@@ -217,7 +217,7 @@ class SelectiveScanMixer(Mixer):
                                                 step.extra["scan_seg_start"], step.extra["scan_seg_row"], segments, self.n, self.n_padded, self.dtype)
         else:
             y = recurrent.selective_scan(conv, dt, dbc, self.rank, self.rank + self.n, self.a, self.skip, proj, self.inner, state, 0, slots,
-                                         step.row_start, rows, self.n, self.n_padded, self.dtype)
+                                         step.row_start, rows, self.n, self.n_padded, self.dtype, precise=self.dtype == torch.float32)
         return ops.linear(y, self.w_o, None, self.dtype, may_leave_partials=True)  # the result is a residual delta
 
 
